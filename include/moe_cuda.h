@@ -1,0 +1,176 @@
+/*
+ * moe_cuda.h -- C ABI of libmoe_cuda: the teacher's mixture-of-experts forward
+ * path (route -> count/scan -> scatter -> grouped SwiGLU products -> combine)
+ * as hand-written CUDA for sm_100a.
+ *
+ * The library replaces, for this path only, the reference's generic Vulkan
+ * dispatch `mda_vkc_run(c, kernel, bufs[], gx, gy, gz, &pc)` (src/vkc.h:93,
+ * src/vkc.c:771-789) and the buffer calls around it.  Each kernel entry point
+ * takes the context, raw device pointers in the binding order of the shader it
+ * replaces, and that shader's push-constant struct by value, unchanged.
+ *
+ * Conventions kept from the reference harness (src/vkc.c:15-20, 528-536):
+ *  - no return values on the data path; the first failure makes the context's
+ *    status sticky, prints one line to stderr, and every later call is a no-op;
+ *  - calls are ordered: each runs after the previous one on the context's
+ *    stream; moe_cuda_flush blocks until the device is idle on that stream;
+ *  - all calls come from one host thread; buffers are caller-owned.
+ * There is no CPU fallback: without a usable CUDA device every call fails.
+ */
+#ifndef MOE_CUDA_H
+#define MOE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- push-constant structs: layout identical to src/pc.h:369-404 -------- */
+#ifndef MDA_PC_H
+#define MDA_PC_NO_SLOT 0xffffffffu /* src/pc.h:6 */
+struct mda_pc_moe_route_t { uint32_t rows, experts, topk, stride; };                 /* src/pc.h:369-374 */
+struct mda_pc_moe_scan_t { uint32_t experts, tile; };                                 /* src/pc.h:376-379 */
+struct mda_pc_moe_scatter_t { uint32_t rows, topk, d8; };                             /* src/pc.h:381-385 */
+struct mda_pc_moe_mm_t { uint32_t m, n, k, sa, sb; };                                 /* src/pc.h:387-393 */
+struct mda_pc_moe_combine_t { uint32_t rows, d, topk, pstride, sg_off, inj_stride, inj_off, hc; }; /* src/pc.h:395-404 */
+struct mda_pc_qwen_elem_t { uint32_t rows, n, astride, ao, bo, op; float scale; };    /* shader/qwen_elem.comp:6-14 */
+struct mda_pc_absmax_t { uint32_t n, slot; };                                          /* shader/absmax.comp:6-9 */
+struct mda_pc_cast_t { uint32_t n, slot; };                                            /* shader/cast_f16.comp:14-17 */
+#endif
+typedef struct mda_pc_moe_route_t moe_pc_route_t;
+typedef struct mda_pc_moe_scan_t moe_pc_scan_t;
+typedef struct mda_pc_moe_scatter_t moe_pc_scatter_t;
+typedef struct mda_pc_moe_mm_t moe_pc_mm_t;
+typedef struct mda_pc_moe_combine_t moe_pc_combine_t;
+typedef struct mda_pc_qwen_elem_t moe_pc_elem_t;
+typedef struct mda_pc_absmax_t moe_pc_absmax_t;
+typedef struct mda_pc_cast_t moe_pc_cast_t;
+
+/* ---- status ------------------------------------------------------------- */
+enum {
+    MOE_OK = 0,
+    MOE_ERR_CUDA = 1,        /* a CUDA runtime/driver call failed */
+    MOE_ERR_ARG = 2,         /* shape or pointer outside what the kernels accept */
+    MOE_ERR_NOMEM = 3,       /* allocation refused */
+    MOE_ERR_ROUTE = 4,       /* a row had fewer than topk selectable logits */
+    MOE_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up */
+    MOE_ERR_COMM = 6,        /* expert-parallel communicator failure */
+    MOE_ERR_UNSUPPORTED = 7  /* device is not sm_100 */
+};
+
+typedef struct moe_cuda_ctx moe_cuda_ctx_t;
+
+/* mda_vkc_init (src/vkc.c:95-161): bind one device and one in-order queue.
+ * stream = an existing cudaStream_t to enqueue on, or NULL to create one.
+ * Returns NULL only if the context object itself cannot be made; otherwise
+ * check moe_cuda_status(). */
+moe_cuda_ctx_t *moe_cuda_create(int device, void *stream);
+void moe_cuda_destroy(moe_cuda_ctx_t *c);
+/* c->fail (src/vkc.h:47): sticky.  Also folds in device-reported refusals
+ * (MOE_ERR_ROUTE, MOE_ERR_TIMEOUT) seen so far; call after moe_cuda_flush for
+ * a definitive answer. */
+int moe_cuda_status(moe_cuda_ctx_t *c);
+const char *moe_cuda_last_error(moe_cuda_ctx_t *c);
+void *moe_cuda_stream(moe_cuda_ctx_t *c);
+/* Test hook for host-side failure injection: the n-th allocation from now
+ * (1 = the next one) is refused as if the device were out of memory. */
+void moe_cuda_fail_alloc_after(moe_cuda_ctx_t *c, int n);
+
+/* ---- buffers: mda_vkc_alloc / alloc_cached / free / fill / copy / write /
+ *      read / flush (src/vkc.h:80-97) ------------------------------------- */
+void *moe_cuda_alloc(moe_cuda_ctx_t *c, size_t bytes);        /* device-local (src/vkc.c:363-366) */
+void *moe_cuda_alloc_pinned(moe_cuda_ctx_t *c, size_t bytes); /* host, page-locked (src/vkc.c:367-374) */
+void moe_cuda_free(moe_cuda_ctx_t *c, void *p);
+void moe_cuda_free_pinned(moe_cuda_ctx_t *c, void *p);
+void moe_cuda_fill(moe_cuda_ctx_t *c, void *dst, size_t bytes, uint32_t word);       /* src/vkc.c:803-815 */
+void moe_cuda_copy(moe_cuda_ctx_t *c, void *dst, const void *src, size_t bytes);     /* device to device, src/vkc.c:791-801 */
+void moe_cuda_write(moe_cuda_ctx_t *c, void *dst, const void *host_src, size_t bytes); /* enqueued; host_src must stay valid until flush unless pageable (then staged) */
+void moe_cuda_read(moe_cuda_ctx_t *c, void *host_dst, const void *src, size_t bytes);  /* blocking, src/vkc.c:817-826 */
+void moe_cuda_flush(moe_cuda_ctx_t *c);                                                /* src/vkc.c:655-668 */
+
+/* ---- the five kernels --------------------------------------------------- */
+/* shader/moe_route.comp (bindings proj, idx, wt, count; call src/qwen.c:799-811).
+ * Candidates are experts e < pc.experts (the shader scans a fixed 512).  Ties go
+ * to the lower expert index.  count[] must be zero on entry (src/qwen.c:794).
+ * Limits: experts <= 512, 1 <= topk <= 16, topk <= experts. */
+void moe_cuda_route(moe_cuda_ctx_t *c, const float *proj, uint32_t *idx, float *wt,
+                    uint32_t *count, struct mda_pc_moe_route_t pc);
+/* shader/moe_scan.comp (bindings count, off, tiles; call src/qwen.c:812-821).
+ * tiles[] entries of unused tiles are left as the caller filled them. */
+void moe_cuda_scan(moe_cuda_ctx_t *c, const uint32_t *count, uint32_t *off, uint32_t *tiles,
+                   struct mda_pc_moe_scan_t pc);
+/* shader/moe_scatter.comp (bindings idx, off, fill, x16, xp, slot; call
+ * src/qwen.c:822-835).  Positions inside an expert are in token order (the
+ * shader's atomic order is arbitrary).  fill[] must be zero on entry and ends
+ * equal to the per-expert counts, as after the shader's atomics.  Uses the
+ * context's scratch memory (grown on demand). */
+void moe_cuda_scatter(moe_cuda_ctx_t *c, const uint32_t *idx, const uint32_t *off,
+                      uint32_t *fill, const void *x16, void *xp, uint32_t *slot,
+                      struct mda_pc_moe_scatter_t pc);
+/* shader/matmul_f16_moe.comp (bindings A, B, C, amax, tiles; wrapper
+ * src/qwen.c:770-786).  C[m x n] fp32 = A[m x k] * B[tiles[y]][n x k]^T /
+ * (scale(sa) * scale(sb)); 128-row tile y is skipped when tiles[y] == ~0.
+ * Requires m % 128 == 0, n % 128 == 0, k % 8 == 0; experts_in_B bounds tiles[]. */
+void moe_cuda_mm(moe_cuda_ctx_t *c, const void *A, const void *B, float *C,
+                 const uint32_t *amax, const uint32_t *tiles, struct mda_pc_moe_mm_t pc,
+                 uint32_t experts_in_B);
+/* shader/moe_combine.comp (bindings wt, slot, y, proj, sh, inj, h; call
+ * src/qwen.c:887-906).  sh == NULL drops the shared-expert term; inj == NULL
+ * means inj = 0 (so hc = 1 gives the plain residual h += acc). */
+void moe_cuda_combine(moe_cuda_ctx_t *c, const float *wt, const uint32_t *slot, const float *y,
+                      const float *proj, const float *sh, const float *inj, float *h,
+                      struct mda_pc_moe_combine_t pc);
+
+/* ---- glue kernels between the two grouped products (unfused mode) ------- */
+void moe_cuda_swiglu(moe_cuda_ctx_t *c, const float *a, float *y, struct mda_pc_qwen_elem_t pc); /* shader/qwen_elem.comp op 0, src/qwen.c:848-857 */
+void moe_cuda_absmax(moe_cuda_ctx_t *c, const float *x, uint32_t *amax, struct mda_pc_absmax_t pc); /* shader/absmax.comp, src/qwen.c:858-867 */
+void moe_cuda_cast_f16(moe_cuda_ctx_t *c, const float *src, void *dst, const uint32_t *amax,
+                       struct mda_pc_cast_t pc); /* shader/cast_f16.comp, src/qwen.c:868-877 */
+
+/* ---- the fused layer: mda_qwen_route_rec + mda_qwen_moe_rec from the first
+ *      grouped product on (src/qwen.c:788-836, 847-906) in one call --------- */
+typedef struct moe_cuda_layer_t {
+    uint32_t rows, d, experts, topk, inter, shared; /* shared = 0: no shared expert */
+    uint32_t pstride;      /* row stride of proj; shared gate logit at column `experts` */
+    uint32_t hc;           /* residual streams; 1 = plain residual */
+    uint32_t inj_stride, inj_off;
+    const float *proj;     /* [rows x pstride] fp32 */
+    const void *x16;       /* [rows x d] fp16 */
+    const void *wgu;       /* [experts][2*inter x d] fp16: gate rows then up rows */
+    const void *wdown;     /* [experts][d x inter] fp16 */
+    const void *wsgu;      /* [2*shared x d] fp16 or NULL */
+    const void *wsdown;    /* [d x shared] fp16 or NULL */
+    const float *inj;      /* or NULL */
+    float *h;              /* [rows x hc x d] fp32, accumulated into */
+    /* optional outputs for inspection (NULL = kept in context scratch) */
+    uint32_t *idx, *slot, *count, *off, *tiles;
+    float *wt;
+    /* optional: y16 [rows x d] fp16 = RMSNorm(x16 + moe(x)) with unit weight;
+     * when set, h may be NULL.  (Residual + norm between stacked layers.) */
+    void *y16;
+    float eps;
+    uint32_t flags;        /* MOE_LAYER_* */
+} moe_cuda_layer_t;
+#define MOE_LAYER_UNFUSED 1u /* run the reference's kernel sequence step by step (fp32 g, absmax rescale) */
+#define MOE_LAYER_YE_F32 2u  /* keep expert outputs fp32 between the down product and the combine */
+
+/* Rows of scratch the layer needs: round128(rows*topk + experts*127), src/qwen.c:68-70. */
+uint32_t moe_cuda_moe_rows(uint32_t rows, uint32_t topk, uint32_t experts);
+void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
+
+/* Per-stage device times of the last moe_cuda_layer call, in milliseconds, in
+ * the order route, scan, scatter, gate_up, down, shared, combine (after
+ * mda_vkc_prof_begin / prof_report, src/vkc.c:595-653).  Enabled with
+ * moe_cuda_prof(c, 1); reading them synchronises the stream. */
+#define MOE_PROF_STAGES 7
+void moe_cuda_prof(moe_cuda_ctx_t *c, int on);
+void moe_cuda_prof_read(moe_cuda_ctx_t *c, float ms[MOE_PROF_STAGES]);
+/* Number of kernels this library has launched on the context so far. */
+uint64_t moe_cuda_launches(moe_cuda_ctx_t *c);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,130 @@
+// Shared declarations of libmoe_cuda's translation units: the context object,
+// status handling and small device helpers.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/moe_cuda.h"
+
+#define MOE_MAX_EXPERTS 512u  // shader/moe_route.comp:24-26, shader/moe_scan.comp:2
+#define MOE_MAX_TOPK 16u      // shader/moe_route.comp:18
+#define MOE_TILE 128u         // MDA_QWEN_TILE, src/qwen.h:14
+
+// Scratch areas inside the context (grown on demand, never shrunk).
+enum { MOE_SCR_SCATTER = 0, MOE_SCR_LAYER = 1, MOE_SCR_STAGE = 2, MOE_SCR_EP = 3, MOE_SCR_COUNT = 4 };
+
+struct moe_tmap_entry {
+    const void *ptr;
+    uint64_t rows, cols;
+    uint32_t box_rows, box_cols;
+    CUtensorMap map;
+};
+
+struct moe_ep_state;  // moe_ep.cu
+
+struct moe_cuda_ctx {
+    int device;
+    int sm_count;
+    cudaStream_t stream;
+    bool own_stream;
+    int status;  // sticky, like mda_vkc_t.fail (src/vkc.h:47)
+    char err[256];
+    // Device-visible status word in mapped pinned memory: kernels record refusals
+    // (MOE_ERR_ROUTE, MOE_ERR_TIMEOUT) here instead of trapping.
+    uint32_t *dev_status_host;
+    uint32_t *dev_status_dev;
+    void *scratch[MOE_SCR_COUNT];
+    size_t scratch_bytes[MOE_SCR_COUNT];
+    moe_tmap_entry tmaps[32];
+    int n_tmaps, next_tmap;
+    void *encode_tiled;  // cuTensorMapEncodeTiled, resolved at create
+    bool prof;
+    cudaEvent_t ev[MOE_PROF_STAGES + 1];
+    bool ev_made, ev_valid;
+    uint64_t launches;
+    int fail_alloc_countdown;
+    bool mm_attr_set[4];
+    moe_ep_state *ep;
+};
+
+void moe_fail(moe_cuda_ctx *c, int code, const char *fmt, ...);
+void *moe_scratch(moe_cuda_ctx *c, int area, size_t bytes);
+bool moe_poll_device_status(moe_cuda_ctx *c);
+void moe_ep_teardown(moe_cuda_ctx *c);
+const CUtensorMap *moe_tmap_2d_f16(moe_cuda_ctx *c, const void *ptr, uint64_t rows, uint64_t cols,
+                                   uint32_t box_rows, uint32_t box_cols);
+
+#define MOE_LIVE(c) ((c) != NULL && (c)->status == MOE_OK)
+
+#define MOE_CUDA_TRY(c, expr)                                                             \
+    do {                                                                                  \
+        cudaError_t e__ = (expr);                                                         \
+        if (e__ != cudaSuccess) {                                                         \
+            moe_fail((c), MOE_ERR_CUDA, "%s:%d: %s", __FILE__, __LINE__,                  \
+                     cudaGetErrorString(e__));                                            \
+            return;                                                                       \
+        }                                                                                 \
+    } while (0)
+
+#define MOE_LAUNCHED(c)                                                                   \
+    do {                                                                                  \
+        (c)->launches += 1;                                                               \
+        MOE_CUDA_TRY((c), cudaGetLastError());                                            \
+    } while (0)
+
+#define MOE_REQUIRE(c, cond, ...)                                                         \
+    do {                                                                                  \
+        if (!(cond)) {                                                                    \
+            moe_fail((c), MOE_ERR_ARG, __VA_ARGS__);                                      \
+            return;                                                                       \
+        }                                                                                 \
+    } while (0)
+
+// Internal launch helpers shared between the ABI entry points and the fused layer.
+void moe_launch_route(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *wt, uint32_t *count,
+                      uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride);
+void moe_launch_scan(moe_cuda_ctx *c, const uint32_t *count, uint32_t *off, uint32_t *tiles,
+                     uint32_t experts, uint32_t tile);
+void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, uint32_t *fill,
+                        const void *x16, void *xp, uint32_t *slot, uint32_t rows, uint32_t topk,
+                        uint32_t d8, uint32_t experts_bound);
+
+enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
+// Grouped product.  mode F32: C fp32 [m x n] = A*B^T * s;  SWIGLU_F16: B holds
+// [gate n/2 rows | up n/2 rows] per expert and C fp16 [m x n/2] = silu(gate)*up;
+// F16: C fp16 [m x n].
+// a_rows = rows A really holds (<= m); rows beyond read as zero.
+void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C,
+                   const uint32_t *amax, const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k,
+                   uint32_t sa, uint32_t sb, uint32_t experts_in_B, uint32_t a_rows);
+
+struct moe_combine_args {
+    const float *wt;
+    const uint32_t *slot;
+    const void *y;       // fp32 or fp16 [M x d]
+    const float *proj;
+    const float *sh;     // fp32 [rows x d] or NULL
+    const float *inj;    // or NULL
+    float *h;            // or NULL when y16 is set
+    const __half *x16;   // residual input for the fused norm (or NULL)
+    __half *y16;         // fused residual + RMSNorm output (or NULL)
+    float eps;
+    uint32_t rows, d, topk, pstride, sg_off, inj_stride, inj_off, hc;
+    bool y_is_f16;
+};
+void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a);
+
+// ---- device helpers -------------------------------------------------------
+__device__ __forceinline__ float moe_slot_scale(const uint32_t *amax, uint32_t s) {
+    // shader/matmul_f16_moe.comp:60-68 = shader/cast_f16.comp:20-28
+    if (s == MDA_PC_NO_SLOT) return 1.0f;
+    uint32_t bits = amax[s];
+    float a = __uint_as_float(bits);
+    if (!(a > 0.0f) || isinf(a)) return 1.0f;
+    return exp2f(141.0f - (float)((bits >> 23) & 0xffu));
+}

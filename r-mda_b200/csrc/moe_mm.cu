@@ -1,0 +1,418 @@
+// Grouped expert products on the 5th-generation tensor cores (sm_100a).
+//
+// C[m0:m0+128, :] = A[m0:m0+128, :k] * B[e]^T for every 128-row tile whose
+// tiles[] entry e is not ~0 -- the tile schedule that the scan kernel builds
+// from the per-expert offsets (shader/matmul_f16_moe.comp:70-78).
+//
+// One persistent CTA per SM walks the (row tile, column tile) list.  Roles:
+//   warp 0     TMA producer: 128x64 fp16 boxes of A and two 128x64 boxes of B
+//              per stage into a 4-stage shared-memory ring (128-byte swizzle);
+//              plain per-CTA loads, never multicast.
+//   warp 1     allocates tensor memory and issues tcgen05.mma (M128 N256 K16,
+//              fp16 x fp16 -> fp32) into one of two 256-column accumulators.
+//   warps 2-5  epilogue: tcgen05.ld the finished accumulator, apply the mode's
+//              epilogue, store; overlaps the next tile's main loop.
+// Modes: F32 (reference semantics: fp32 C, power-of-two slot scale), SWIGLU_F16
+// (B tile = 128 gate rows + the matching 128 up rows; C = fp16 silu(gate)*up,
+// i.e. shader/qwen_elem.comp op 0 + the fp16 store fused into the product) and
+// F16 (fp16 C).  Every spin on an mbarrier is bounded; on timeout the kernel
+// records MOE_ERR_TIMEOUT in the context's status word and unwinds.
+#include "moe_common.cuh"
+
+namespace {
+
+constexpr uint32_t BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr uint32_t A_BYTES = BM * BK * 2;       // 16 KB
+constexpr uint32_t BH_BYTES = 128 * BK * 2;     // 16 KB: half of the B tile
+constexpr uint32_t STAGE_BYTES = A_BYTES + 2 * BH_BYTES;
+constexpr uint32_t MM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint64_t WAIT_NS = 2000000000ull;     // bound of any single wait
+
+struct __align__(8) MmBarriers {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort;
+};
+constexpr uint32_t MM_SMEM = STAGES * STAGE_BYTES + sizeof(MmBarriers) + 1024;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  False = gave up (own timeout, or another role raised abort).
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort, uint32_t *status,
+                                       uint32_t site) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        spins += 1;
+        if ((spins & 0xffu) == 0) {
+            if (*abort != 0) return false;
+            uint64_t now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > WAIT_NS) {
+                *abort = 1;
+                atomicCAS(status, 0u, (uint32_t)MOE_ERR_TIMEOUT | (site << 8));
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :
+        : "r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row
+// groups 1024 bytes apart, descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: D fp32, A/B fp16, both K-major, M 128.
+__device__ __forceinline__ uint32_t umma_idesc(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        :
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+struct MmArgs {
+    void *C;
+    const uint32_t *amax;
+    const uint32_t *tiles;
+    uint32_t m, n, k, sa, sb, experts_in_B;
+    uint32_t *status;
+};
+
+struct WorkItem {
+    uint32_t mt, nt, e, nvalid;
+    int32_t rb0, rb1;
+};
+
+template <int MODE>
+__device__ __forceinline__ bool mm_work(const MmArgs &a, uint32_t w, uint32_t nt_count, WorkItem &it) {
+    it.mt = w / nt_count;
+    it.nt = w - it.mt * nt_count;
+    it.e = a.tiles[it.mt];
+    if (it.e >= a.experts_in_B) return false;  // ~0: unused tile (matmul_f16_moe.comp:72-74)
+    if (MODE == MOE_MM_SWIGLU_F16) {
+        it.nvalid = BN;
+        it.rb0 = (int32_t)(it.e * a.n + it.nt * 128u);
+        it.rb1 = (int32_t)(it.e * a.n + a.n / 2u + it.nt * 128u);
+    } else {
+        uint32_t n0 = it.nt * BN;
+        it.nvalid = a.n - n0 < BN ? a.n - n0 : BN;  // 128 or 256
+        it.rb0 = (int32_t)(it.e * a.n + n0);
+        it.rb1 = it.rb0 + 128;
+    }
+    return true;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(MM_THREADS, 1)
+moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, MmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    MmBarriers *bars = reinterpret_cast<MmBarriers *>(smem + STAGES * STAGE_BYTES);
+    const uint32_t stage0 = smem_u32(smem);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    volatile uint32_t *abort = &bars->abort;
+
+    const uint32_t nt_count = MODE == MOE_MM_SWIGLU_F16 ? a.n / BN : (a.n + BN - 1) / BN;
+    const uint32_t total = (a.m / BM) * nt_count;
+    const uint32_t kblocks = (a.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < STAGES; s += 1) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (uint32_t s = 0; s < 2; s += 1) {
+            mbar_init(smem_u32(&bars->tmem_full[s]), 1);
+            mbar_init(smem_u32(&bars->tmem_empty[s]), 128);
+        }
+        bars->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            uint32_t issued = 0;  // bit s set once stage s has a load in flight or done
+            uint32_t last_par = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                WorkItem it;
+                if (!mm_work<MODE>(a, w, nt_count, it)) continue;
+                for (uint32_t kb = 0; kb < kblocks; kb += 1) {
+                    if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    uint32_t full = smem_u32(&bars->full[s]);
+                    uint32_t base = stage0 + s * STAGE_BYTES;
+                    mbar_expect_tx(full, A_BYTES + (it.nvalid == BN ? 2 * BH_BYTES : BH_BYTES));
+                    tma_load_2d(base, &tmA, full, (int32_t)(kb * BK), (int32_t)(it.mt * BM));
+                    tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
+                    if (it.nvalid == BN) tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb1);
+                    issued |= 1u << s;
+                    last_par = (last_par & ~(1u << s)) | (ph << s);
+                    s += 1;
+                    if (s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // unwinding: give copies already issued a bounded time to land
+                for (uint32_t q = 0; q < STAGES; q += 1) {
+                    if (((issued >> q) & 1u) == 0) continue;
+                    for (uint32_t spin = 0; spin < (1u << 16); spin += 1) {
+                        if (mbar_try_wait(smem_u32(&bars->full[q]), (last_par >> q) & 1u)) break;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0, n_item = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                WorkItem it;
+                if (!mm_work<MODE>(a, w, nt_count, it)) continue;
+                uint32_t as = n_item & 1u, aph = (n_item >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&bars->tmem_empty[as]), aph ^ 1u, abort, a.status, 2)) break;
+                tc_fence_after();
+                uint32_t tmem_d = tmem_base + as * BN;
+                uint32_t idesc = umma_idesc(it.nvalid);
+                for (uint32_t kb = 0; kb < kblocks; kb += 1) {
+                    if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort, a.status, 3)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint32_t base = stage0 + s * STAGE_BYTES;
+                    uint64_t ad = umma_desc(base), bd = umma_desc(base + A_BYTES);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
+                        // +32 bytes per K=16 step inside the 128-byte swizzle row
+                        umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&bars->empty[s]));  // frees the stage when these MMAs retire
+                    s += 1;
+                    if (s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(smem_u32(&bars->tmem_full[as]));
+                n_item += 1;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const uint32_t q = warp & 3u;  // TMEM lane quarter this warp may read
+        float scale = 1.0f;
+        if (MODE == MOE_MM_F32) scale = 1.0f / (moe_slot_scale(a.amax, a.sa) * moe_slot_scale(a.amax, a.sb));
+        uint32_t n_item = 0;
+        for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
+            WorkItem it;
+            if (!mm_work<MODE>(a, w, nt_count, it)) continue;
+            uint32_t as = n_item & 1u, aph = (n_item >> 1) & 1u;
+            if (!mbar_wait(smem_u32(&bars->tmem_full[as]), aph, abort, a.status, 4)) break;
+            tc_fence_after();
+            uint32_t taddr = tmem_base + as * BN + ((q * 32u) << 16);
+            size_t row = (size_t)it.mt * BM + q * 32u + lane;
+            if (MODE == MOE_MM_SWIGLU_F16) {
+                __half *out = reinterpret_cast<__half *>(a.C) + row * (a.n / 2u) + it.nt * 128u;
+#pragma unroll 1
+                for (uint32_t cch = 0; cch < 4; cch += 1) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(taddr + cch * 32u, g);
+                    tmem_ld32(taddr + 128u + cch * 32u, u);
+                    tmem_ld_wait();
+                    uint32_t o[16];
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; j += 1) {
+                        float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+                        float h0 = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(u[2 * j]);
+                        float h1 = __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(u[2 * j + 1]);
+                        o[j] = pack_h2(h0, h1);
+                    }
+                    uint4 *dst = reinterpret_cast<uint4 *>(out + cch * 32u);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; j += 1) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                }
+            } else if (MODE == MOE_MM_F16) {
+                __half *out = reinterpret_cast<__half *>(a.C) + row * a.n + it.nt * BN;
+#pragma unroll 1
+                for (uint32_t cch = 0; cch < it.nvalid / 32u; cch += 1) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + cch * 32u, v);
+                    tmem_ld_wait();
+                    uint4 *dst = reinterpret_cast<uint4 *>(out + cch * 32u);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; j += 1) {
+                        dst[j] = make_uint4(pack_h2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
+                                            pack_h2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
+                                            pack_h2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
+                                            pack_h2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
+                    }
+                }
+            } else {
+                float *out = reinterpret_cast<float *>(a.C) + row * a.n + it.nt * BN;
+#pragma unroll 1
+                for (uint32_t cch = 0; cch < it.nvalid / 32u; cch += 1) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + cch * 32u, v);
+                    tmem_ld_wait();
+                    float4 *dst = reinterpret_cast<float4 *>(out + cch * 32u);
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; j += 1) {
+                        dst[j] = make_float4(__uint_as_float(v[4 * j]) * scale, __uint_as_float(v[4 * j + 1]) * scale,
+                                             __uint_as_float(v[4 * j + 2]) * scale, __uint_as_float(v[4 * j + 3]) * scale);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+            n_item += 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int MODE>
+void mm_launch(moe_cuda_ctx *c, const CUtensorMap *tmA, const CUtensorMap *tmB, const MmArgs &a, uint32_t grid) {
+    if (!c->mm_attr_set[MODE]) {
+        MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_mm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM));
+        c->mm_attr_set[MODE] = true;
+    }
+    moe_mm_kernel<MODE><<<grid, MM_THREADS, MM_SMEM, c->stream>>>(*tmA, *tmB, a);
+    MOE_LAUNCHED(c);
+}
+
+}  // namespace
+
+void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C, const uint32_t *amax,
+                   const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k, uint32_t sa, uint32_t sb,
+                   uint32_t experts_in_B, uint32_t a_rows) {
+    if (!MOE_LIVE(c)) return;
+    MOE_REQUIRE(c, A != NULL && B != NULL && C != NULL && tiles != NULL, "mm: null buffer");
+    MOE_REQUIRE(c, a_rows >= 1 && a_rows <= m, "mm: a_rows %u outside 1..m", a_rows);
+    MOE_REQUIRE(c, m % BM == 0, "mm: m %u not a multiple of 128", m);
+    MOE_REQUIRE(c, n % 128u == 0 && n >= 128u, "mm: n %u not a multiple of 128", n);
+    MOE_REQUIRE(c, mode != MOE_MM_SWIGLU_F16 || n % 256u == 0, "mm: fused SwiGLU needs inter %% 128 == 0 (n = %u)", n);
+    MOE_REQUIRE(c, k % 8u == 0 && k >= 8u, "mm: k %u not a multiple of 8", k);
+    MOE_REQUIRE(c, experts_in_B >= 1 && (uint64_t)experts_in_B * n < (1ull << 31), "mm: expert count");
+    MOE_REQUIRE(c, (sa == MDA_PC_NO_SLOT && sb == MDA_PC_NO_SLOT) || amax != NULL, "mm: scale slot without amax");
+    MOE_REQUIRE(c, ((uintptr_t)C & 15) == 0, "mm: C not 16-byte aligned");
+    const CUtensorMap *tmA = moe_tmap_2d_f16(c, A, a_rows, k, 128, BK);
+    const CUtensorMap *tmB = moe_tmap_2d_f16(c, B, (uint64_t)experts_in_B * n, k, 128, BK);
+    if (tmA == NULL || tmB == NULL) return;
+    MmArgs a;
+    a.C = C;
+    a.amax = amax;
+    a.tiles = tiles;
+    a.m = m;
+    a.n = n;
+    a.k = k;
+    a.sa = sa;
+    a.sb = sb;
+    a.experts_in_B = experts_in_B;
+    a.status = c->dev_status_dev;
+    uint32_t nt = mode == MOE_MM_SWIGLU_F16 ? n / BN : (n + BN - 1) / BN;
+    uint64_t total = (uint64_t)(m / BM) * nt;
+    uint32_t grid = total < (uint64_t)c->sm_count ? (uint32_t)total : (uint32_t)c->sm_count;
+    if (mode == MOE_MM_F32) mm_launch<MOE_MM_F32>(c, tmA, tmB, a, grid);
+    else if (mode == MOE_MM_SWIGLU_F16) mm_launch<MOE_MM_SWIGLU_F16>(c, tmA, tmB, a, grid);
+    else mm_launch<MOE_MM_F16>(c, tmA, tmB, a, grid);
+}
+
+extern "C" void moe_cuda_mm(moe_cuda_ctx_t *c, const void *A, const void *B, float *C, const uint32_t *amax,
+                            const uint32_t *tiles, struct mda_pc_moe_mm_t pc, uint32_t experts_in_B) {
+    moe_launch_mm(c, MOE_MM_F32, A, B, C, amax, tiles, pc.m, pc.n, pc.k, pc.sa, pc.sb, experts_in_B, pc.m);
+}

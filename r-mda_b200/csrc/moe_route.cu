@@ -1,0 +1,165 @@
+// Router top-k and the per-expert scan: CUDA for sm_100a.
+//
+// route: one warp per row (shader/moe_route.comp uses one 32-lane subgroup per
+// row).  Lane l holds logits e = 4*l + 128*j + {0..3}, j < 4, fetched with
+// 128-bit loads; k rounds of (lane-local best, warp arg-max by shuffle) pick
+// the largest remaining logit, ties to the lower expert index -- the net rule of
+// the shader's subgroupMax / subgroupMin pair (:30-50).
+#include "moe_common.cuh"
+
+#define ROUTE_WARPS 8
+#define ROUTE_SENTINEL -3.0e38f  // shader/moe_route.comp:31
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const float *__restrict__ proj, uint32_t *__restrict__ idx, float *__restrict__ wt,
+                 uint32_t *__restrict__ count, uint32_t rows, uint32_t experts, uint32_t topk,
+                 uint32_t stride, uint32_t *status, int vec_ok) {
+    uint32_t lane = threadIdx.x & 31u;
+    uint32_t warp = threadIdx.x >> 5;
+    uint32_t nwarps = gridDim.x * ROUTE_WARPS;
+    for (uint32_t r = blockIdx.x * ROUTE_WARPS + warp; r < rows; r += nwarps) {
+        const float *row = proj + (size_t)r * stride;
+        float l[16];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; j += 1) {
+            uint32_t e0 = 4u * lane + 128u * j;
+            if (vec_ok && e0 + 3u < experts) {
+                float4 v = __ldg(reinterpret_cast<const float4 *>(row + e0));
+                l[4 * j + 0] = v.x;
+                l[4 * j + 1] = v.y;
+                l[4 * j + 2] = v.z;
+                l[4 * j + 3] = v.w;
+            } else {
+#pragma unroll
+                for (uint32_t q = 0; q < 4; q += 1) {
+                    l[4 * j + q] = e0 + q < experts ? __ldg(row + e0 + q) : ROUTE_SENTINEL;
+                }
+            }
+        }
+        uint32_t taken = 0;
+        float my_v = 0.0f;      // lane k keeps the k-th selected logit
+        uint32_t my_e = ~0u;
+        float v0 = 0.0f;
+        bool bad = false;
+        for (uint32_t k = 0; k < topk; k += 1) {
+            float lb = ROUTE_SENTINEL;
+            uint32_t li = ~0u;
+#pragma unroll
+            for (uint32_t j = 0; j < 16; j += 1) {
+                // ascending expert index inside the lane: q fastest, then the 128-blocks
+                uint32_t e = 4u * lane + 128u * (j >> 2) + (j & 3u);
+                if (((taken >> j) & 1u) == 0u && l[j] > lb) {  // strict >: first of equals (:34)
+                    lb = l[j];
+                    li = e;
+                }
+            }
+            // warp arg-max on (value desc, index asc)
+            float gm = lb;
+            uint32_t gi = li;
+#pragma unroll
+            for (uint32_t o = 16; o > 0; o >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, gm, o);
+                uint32_t oi = __shfl_xor_sync(0xffffffffu, gi, o);
+                if (ov > gm || (ov == gm && oi < gi)) {
+                    gm = ov;
+                    gi = oi;
+                }
+            }
+            if (gi == ~0u) {
+                bad = true;
+            } else if (((gi & 127u) >> 2) == lane) {
+                taken |= 1u << (((gi >> 7) << 2) | (gi & 3u));  // :45-47
+            }
+            if (k == 0) v0 = gm;
+            if (lane == k) {
+                my_v = gm;
+                my_e = gi;
+            }
+        }
+        if (bad) {
+            if (lane == 0) atomicCAS(status, 0u, (uint32_t)MOE_ERR_ROUTE | (r << 8));
+            continue;  // the shader would index count[~0u] here; refuse instead
+        }
+        // :52-60: z accumulated k = 0..topk-1 in fp32, then each weight
+        float t = lane < topk ? expf(my_v - v0) : 0.0f;
+        float z = 0.0f;
+        for (uint32_t k = 0; k < topk; k += 1) z += __shfl_sync(0xffffffffu, t, k);
+        if (lane < topk) {
+            idx[(size_t)r * topk + lane] = my_e;
+            wt[(size_t)r * topk + lane] = t / z;
+            atomicAdd(&count[my_e], 1u);
+        }
+    }
+}
+
+void moe_launch_route(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *wt, uint32_t *count,
+                      uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride) {
+    if (!MOE_LIVE(c)) return;
+    MOE_REQUIRE(c, experts >= 1 && experts <= MOE_MAX_EXPERTS, "route: experts %u outside 1..512", experts);
+    MOE_REQUIRE(c, topk >= 1 && topk <= MOE_MAX_TOPK && topk <= experts, "route: topk %u outside 1..min(16, experts)", topk);
+    MOE_REQUIRE(c, stride >= experts, "route: stride %u < experts %u", stride, experts);
+    MOE_REQUIRE(c, proj != NULL && idx != NULL && wt != NULL && count != NULL, "route: null buffer");
+    if (rows == 0) return;
+    int vec_ok = ((uintptr_t)proj % 16 == 0) && (stride % 4 == 0);
+    uint32_t blocks = (rows + ROUTE_WARPS - 1) / ROUTE_WARPS;
+    uint32_t cap = (uint32_t)c->sm_count * 8u;
+    if (blocks > cap) blocks = cap;
+    moe_route_kernel<<<blocks, ROUTE_WARPS * 32, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride,
+                                                                 c->dev_status_dev, vec_ok);
+    MOE_LAUNCHED(c);
+}
+
+extern "C" void moe_cuda_route(moe_cuda_ctx_t *c, const float *proj, uint32_t *idx, float *wt, uint32_t *count,
+                               struct mda_pc_moe_route_t pc) {
+    moe_launch_route(c, proj, idx, wt, count, pc.rows, pc.experts, pc.topk, pc.stride);
+}
+
+// shader/moe_scan.comp:14-38: one 512-thread block; pad each count to the tile,
+// exclusive prefix sum, one tiles[] entry per padded tile.
+__global__ void __launch_bounds__(512)
+moe_scan_kernel(const uint32_t *__restrict__ count, uint32_t *__restrict__ off, uint32_t *__restrict__ tiles,
+                uint32_t experts, uint32_t tile) {
+    __shared__ uint32_t wsum[16];
+    uint32_t e = threadIdx.x;
+    uint32_t lane = e & 31u, warp = e >> 5;
+    uint32_t p = 0;
+    if (e < experts) p = (count[e] + tile - 1u) / tile * tile;  // :19
+    uint32_t incl = p;
+#pragma unroll
+    for (uint32_t o = 1; o < 32; o <<= 1) {
+        uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t w = lane < 16 ? wsum[lane] : 0;
+#pragma unroll
+        for (uint32_t o = 1; o < 16; o <<= 1) {
+            uint32_t v = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += v;
+        }
+        if (lane < 16) wsum[lane] = w;
+    }
+    __syncthreads();
+    uint32_t lo = incl - p + (warp > 0 ? wsum[warp - 1] : 0);  // :31
+    if (e < experts) {
+        off[e] = lo;  // :33
+        for (uint32_t t = lo / tile; t < (lo + p) / tile; t += 1) tiles[t] = e;  // :34-36
+    }
+}
+
+void moe_launch_scan(moe_cuda_ctx *c, const uint32_t *count, uint32_t *off, uint32_t *tiles, uint32_t experts,
+                     uint32_t tile) {
+    if (!MOE_LIVE(c)) return;
+    MOE_REQUIRE(c, experts >= 1 && experts <= MOE_MAX_EXPERTS, "scan: experts %u outside 1..512", experts);
+    MOE_REQUIRE(c, tile >= 1, "scan: tile 0");
+    MOE_REQUIRE(c, count != NULL && off != NULL && tiles != NULL, "scan: null buffer");
+    moe_scan_kernel<<<1, 512, 0, c->stream>>>(count, off, tiles, experts, tile);
+    MOE_LAUNCHED(c);
+}
+
+extern "C" void moe_cuda_scan(moe_cuda_ctx_t *c, const uint32_t *count, uint32_t *off, uint32_t *tiles,
+                              struct mda_pc_moe_scan_t pc) {
+    moe_launch_scan(c, count, off, tiles, pc.experts, pc.tile);
+}

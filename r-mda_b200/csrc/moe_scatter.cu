@@ -1,0 +1,138 @@
+// Token permutation into expert-contiguous order: CUDA for sm_100a.
+//
+// The reference (shader/moe_scatter.comp:22-27) hands out positions with an
+// atomic per expert, so its order inside an expert depends on scheduling.  Here
+// the position of pair pr = (row, j) is
+//     off[e] + #{pr' < pr : idx[pr'] == e},
+// i.e. stable by token index, computed without any atomic on the order:
+//   1. hist:    blocks of 64 consecutive pairs count their pairs per expert;
+//   2. colscan: exclusive prefix sum of those counts over the blocks, per expert;
+//   3. place:   each block ranks its own 64 pairs in order, adds the block base,
+//               writes slot[], and its 8 warps copy the rows with 128-bit accesses.
+// The (blocks x experts) table of steps 1-2 lives in context scratch memory.
+#include "moe_common.cuh"
+
+#define SC_PAIRS 64u    // pairs per block
+#define SC_THREADS 256u
+
+__global__ void __launch_bounds__(SC_PAIRS)
+moe_scatter_hist_kernel(const uint32_t *__restrict__ idx, uint32_t *__restrict__ hist, uint32_t pairs,
+                        uint32_t ebound, uint32_t *status) {
+    extern __shared__ uint32_t sh[];
+    for (uint32_t e = threadIdx.x; e < ebound; e += SC_PAIRS) sh[e] = 0;
+    __syncthreads();
+    uint32_t pr = blockIdx.x * SC_PAIRS + threadIdx.x;
+    if (pr < pairs) {
+        uint32_t e = idx[pr];
+        if (e < ebound) {
+            atomicAdd(&sh[e], 1u);  // a count: order is irrelevant
+        } else {
+            atomicCAS(status, 0u, (uint32_t)MOE_ERR_ARG | (1u << 8));
+        }
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < ebound; e += SC_PAIRS) hist[(size_t)blockIdx.x * ebound + e] = sh[e];
+}
+
+// One block per 32 experts; thread (seg, el) sums a contiguous segment of block
+// rows for expert el, the 32 segment sums are scanned, then each thread rewrites
+// its segment as exclusive prefixes.  fill[e] receives the expert's total.
+__global__ void __launch_bounds__(1024)
+moe_scatter_colscan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fill, uint32_t nblocks,
+                           uint32_t ebound) {
+    __shared__ uint32_t seg_sum[32][33];
+    uint32_t el = threadIdx.x & 31u, seg = threadIdx.x >> 5;
+    uint32_t e = blockIdx.x * 32u + el;
+    uint32_t per = (nblocks + 31u) / 32u;
+    uint32_t b0 = seg * per, b1 = min(b0 + per, nblocks);
+    uint32_t s = 0;
+    if (e < ebound) {
+        for (uint32_t b = b0; b < b1; b += 1) s += hist[(size_t)b * ebound + e];
+    }
+    seg_sum[seg][el] = s;
+    __syncthreads();
+    uint32_t base = 0;
+    for (uint32_t q = 0; q < seg; q += 1) base += seg_sum[q][el];
+    if (e < ebound) {
+        uint32_t run = base;
+        for (uint32_t b = b0; b < b1; b += 1) {
+            uint32_t v = hist[(size_t)b * ebound + e];
+            hist[(size_t)b * ebound + e] = run;
+            run += v;
+        }
+        if (seg == 31 && fill != NULL) fill[e] += run;  // state after the shader's atomics (:25)
+    }
+}
+
+__global__ void __launch_bounds__(SC_THREADS)
+moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__restrict__ off,
+                         const uint32_t *__restrict__ base, const uint4 *__restrict__ x16,
+                         uint4 *__restrict__ xp, uint32_t *__restrict__ slot, uint32_t pairs, uint32_t topk,
+                         uint32_t d8, uint32_t ebound) {
+    __shared__ uint32_t s_e[SC_PAIRS];
+    __shared__ uint32_t s_slot[SC_PAIRS];
+    uint32_t p0 = blockIdx.x * SC_PAIRS;
+    uint32_t np = min(SC_PAIRS, pairs - p0);
+    if (threadIdx.x < SC_PAIRS) s_e[threadIdx.x] = threadIdx.x < np ? idx[p0 + threadIdx.x] : ~0u;
+    __syncthreads();
+    if (threadIdx.x < np) {
+        uint32_t e = s_e[threadIdx.x];
+        if (e < ebound) {
+            uint32_t rank = 0;
+            for (uint32_t q = 0; q < threadIdx.x; q += 1) rank += s_e[q] == e;
+            uint32_t p = off[e] + base[(size_t)blockIdx.x * ebound + e] + rank;
+            s_slot[threadIdx.x] = p;
+            slot[p0 + threadIdx.x] = p;  // :27
+        } else {
+            s_slot[threadIdx.x] = ~0u;
+        }
+    }
+    __syncthreads();
+    uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    for (uint32_t q = warp; q < np; q += SC_THREADS / 32u) {
+        uint32_t p = s_slot[q];
+        if (p == ~0u) continue;
+        uint32_t r = (p0 + q) / topk;  // :20
+        const uint4 *src = x16 + (size_t)r * d8;
+        uint4 *dst = xp + (size_t)p * d8;
+        uint32_t i = lane;
+        for (; i + 96u < d8; i += 128u) {  // four 16-byte loads in flight per lane
+            uint4 a = __ldg(src + i), b = __ldg(src + i + 32u), c2 = __ldg(src + i + 64u), d2 = __ldg(src + i + 96u);
+            dst[i] = a;
+            dst[i + 32u] = b;
+            dst[i + 64u] = c2;
+            dst[i + 96u] = d2;
+        }
+        for (; i < d8; i += 32u) dst[i] = __ldg(src + i);  // :30-32
+    }
+}
+
+void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, uint32_t *fill, const void *x16,
+                        void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t ebound) {
+    if (!MOE_LIVE(c)) return;
+    MOE_REQUIRE(c, idx != NULL && off != NULL && x16 != NULL && xp != NULL && slot != NULL, "scatter: null buffer");
+    MOE_REQUIRE(c, topk >= 1 && d8 >= 1 && ebound >= 1 && ebound <= MOE_MAX_EXPERTS, "scatter: bad shape");
+    MOE_REQUIRE(c, ((uintptr_t)x16 & 15) == 0 && ((uintptr_t)xp & 15) == 0, "scatter: rows not 16-byte aligned");
+    uint64_t pairs64 = (uint64_t)rows * topk;
+    MOE_REQUIRE(c, pairs64 < (1ull << 31), "scatter: too many pairs");
+    uint32_t pairs = (uint32_t)pairs64;
+    if (pairs == 0) return;
+    uint32_t nblocks = (pairs + SC_PAIRS - 1) / SC_PAIRS;
+    uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)nblocks * ebound * sizeof(uint32_t));
+    if (hist == NULL) return;
+    moe_scatter_hist_kernel<<<nblocks, SC_PAIRS, ebound * sizeof(uint32_t), c->stream>>>(idx, hist, pairs, ebound,
+                                                                                         c->dev_status_dev);
+    MOE_LAUNCHED(c);
+    moe_scatter_colscan_kernel<<<(ebound + 31u) / 32u, 1024, 0, c->stream>>>(hist, fill, nblocks, ebound);
+    MOE_LAUNCHED(c);
+    moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp,
+                                                                    slot, pairs, topk, d8, ebound);
+    MOE_LAUNCHED(c);
+}
+
+extern "C" void moe_cuda_scatter(moe_cuda_ctx_t *c, const uint32_t *idx, const uint32_t *off, uint32_t *fill,
+                                 const void *x16, void *xp, uint32_t *slot, struct mda_pc_moe_scatter_t pc) {
+    // The push constants carry no expert count (src/pc.h:381-385); the table is
+    // sized for the reference's limit of 512.
+    moe_launch_scatter(c, idx, off, fill, x16, xp, slot, pc.rows, pc.topk, pc.d8, MOE_MAX_EXPERTS);
+}
