@@ -123,6 +123,29 @@ void moe_cuda_combine(moe_cuda_ctx_t *c, const float *wt, const uint32_t *slot, 
                       const float *proj, const float *sh, const float *inj, float *h,
                       struct mda_pc_moe_combine_t pc);
 
+/* No counterpart in the reference.  moe_cuda_scatter for callers that must not
+ * allocate device memory on the data path: a host that gave its whole device
+ * budget to weights and pre-sized buffers at start-up (the reference itself
+ * allocates all scratch once, in mda_qwen_scratch, and nothing on the path
+ * allocates), or a loop that cannot afford the device-wide synchronisation a
+ * cudaMalloc implies.  The per-block expert table that moe_cuda_scatter keeps in
+ * growable context scratch lives here in a fixed array inside the library's
+ * device image, so this call performs no cudaMalloc, cudaFree or other
+ * allocating call.  Same arguments and results as moe_cuda_scatter, plus the
+ * expert count (idx values must be < experts).
+ *  - Limit: ceil(rows*topk/64) * experts <= MOE_NOALLOC_SCATTER_WORDS; larger
+ *    calls are refused with MOE_ERR_ARG (sticky, like every refusal).
+ *  - Every GPU that loads the library holds the 8 MiB table until exit.
+ *  - The first call on a device looks up the table's device address (a query,
+ *    not an allocation); make that first call before any stream capture starts.
+ *  - All calls on a device share the one table: calls that overlap on the GPU
+ *    (different streams or contexts) race.  Nothing in it has to be cleared
+ *    between calls; each call overwrites what it reads. */
+#define MOE_NOALLOC_SCATTER_WORDS (2u << 20)
+void moe_cuda_scatter_noalloc(moe_cuda_ctx_t *c, const uint32_t *idx, const uint32_t *off,
+                              uint32_t *fill, const void *x16, void *xp, uint32_t *slot,
+                              struct mda_pc_moe_scatter_t pc, uint32_t experts);
+
 /* ---- glue kernels between the two grouped products (unfused mode) ------- */
 void moe_cuda_swiglu(moe_cuda_ctx_t *c, const float *a, float *y, struct mda_pc_qwen_elem_t pc); /* shader/qwen_elem.comp op 0, src/qwen.c:848-857 */
 void moe_cuda_absmax(moe_cuda_ctx_t *c, const float *x, uint32_t *amax, struct mda_pc_absmax_t pc); /* shader/absmax.comp, src/qwen.c:858-867 */

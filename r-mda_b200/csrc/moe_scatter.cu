@@ -136,3 +136,59 @@ extern "C" void moe_cuda_scatter(moe_cuda_ctx_t *c, const uint32_t *idx, const u
     // sized for the reference's limit of 512.
     moe_launch_scatter(c, idx, off, fill, x16, xp, slot, pc.rows, pc.topk, pc.d8, MOE_MAX_EXPERTS);
 }
+
+// ---- scatter without any allocation ---------------------------------------
+// Same three kernels, but the (blocks x experts) table lives in a fixed array in
+// device global memory that the library image carries, instead of context
+// scratch that grows with cudaMalloc.  Every GPU that loads the library holds
+// these MOE_NOALLOC_SCATTER_WORDS * 4 bytes until the process exits.
+static __device__ __align__(256) uint32_t g_scatter_noalloc_table[MOE_NOALLOC_SCATTER_WORDS];
+
+#define MOE_NOALLOC_MAX_DEVICES 64
+// In host code the array's name is only a handle for the runtime, not a device
+// address; the address each device gives it is looked up once per device.
+static uint32_t *g_scatter_noalloc_ptr[MOE_NOALLOC_MAX_DEVICES];
+
+extern "C" void moe_cuda_scatter_noalloc(moe_cuda_ctx_t *c, const uint32_t *idx, const uint32_t *off,
+                                         uint32_t *fill, const void *x16, void *xp, uint32_t *slot,
+                                         struct mda_pc_moe_scatter_t pc, uint32_t experts) {
+    if (!MOE_LIVE(c)) return;
+    MOE_REQUIRE(c, c->device >= 0 && c->device < MOE_NOALLOC_MAX_DEVICES, "scatter_noalloc: device %d outside 0..63", c->device);
+    MOE_REQUIRE(c, experts >= 1 && experts <= MOE_MAX_EXPERTS, "scatter_noalloc: experts %u outside 1..512", experts);
+    uint64_t pairs = (uint64_t)pc.rows * pc.topk;
+    uint64_t nblocks = (pairs + SC_PAIRS - 1) / SC_PAIRS;
+    MOE_REQUIRE(c, nblocks * experts <= (uint64_t)MOE_NOALLOC_SCATTER_WORDS,
+                "scatter_noalloc: ceil(rows*topk/64)*experts = %llu exceeds the fixed table of %u words; "
+                "use moe_cuda_scatter or fewer rows per call",
+                (unsigned long long)(nblocks * experts), (unsigned)MOE_NOALLOC_SCATTER_WORDS);
+    if (g_scatter_noalloc_ptr[c->device] == NULL) {
+        // First call on this device: resolve the table's device address with that
+        // device current.  This is a runtime query, not an allocation.
+        int cur = -1;
+        MOE_CUDA_TRY(c, cudaGetDevice(&cur));
+        if (cur != c->device) MOE_CUDA_TRY(c, cudaSetDevice(c->device));
+        uint32_t *p = NULL;
+        cudaError_t e = cudaGetSymbolAddress((void **)&p, g_scatter_noalloc_table);
+        if (cur != c->device) cudaSetDevice(cur);
+        if (e != cudaSuccess || p == NULL) {
+            moe_fail(c, MOE_ERR_CUDA, "scatter_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return;
+        }
+        g_scatter_noalloc_ptr[c->device] = p;
+    }
+    uint32_t *table = g_scatter_noalloc_ptr[c->device];
+    MOE_REQUIRE(c, idx != NULL && off != NULL && x16 != NULL && xp != NULL && slot != NULL, "scatter_noalloc: null buffer");
+    MOE_REQUIRE(c, pc.topk >= 1 && pc.d8 >= 1, "scatter_noalloc: bad shape");
+    MOE_REQUIRE(c, ((uintptr_t)x16 & 15) == 0 && ((uintptr_t)xp & 15) == 0, "scatter_noalloc: rows not 16-byte aligned");
+    if (pairs == 0) return;
+    // The table keeps the previous call's contents; nothing has to start at zero
+    // because the hist kernel writes every entry the later kernels read.
+    moe_scatter_hist_kernel<<<(uint32_t)nblocks, SC_PAIRS, experts * sizeof(uint32_t), c->stream>>>(
+        idx, table, (uint32_t)pairs, experts, c->dev_status_dev);
+    MOE_LAUNCHED(c);
+    moe_scatter_colscan_kernel<<<(experts + 31u) / 32u, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts);
+    MOE_LAUNCHED(c);
+    moe_scatter_place_kernel<<<(uint32_t)nblocks, SC_THREADS, 0, c->stream>>>(
+        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts);
+    MOE_LAUNCHED(c);
+}

@@ -98,6 +98,7 @@ def lib() -> C.CDLL:
         L.moe_cuda_scan.argtypes = [vp, vp, vp, vp, PcScan]
         L.moe_cuda_scatter.argtypes = [vp, vp, vp, vp, vp, vp, vp, PcScatter]
         L.moe_cuda_mm.argtypes = [vp, vp, vp, vp, vp, vp, PcMm, u32]
+        L.moe_cuda_scatter_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, PcScatter, u32]
         L.moe_cuda_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, PcCombine]
         L.moe_cuda_swiglu.argtypes = [vp, vp, vp, PcElem]
         L.moe_cuda_absmax.argtypes = [vp, vp, vp, PcSlot]
@@ -225,6 +226,10 @@ class Ctx:
     def scatter(self, idx, off, fill, x16, xp, slot, rows, topk, d8):
         lib().moe_cuda_scatter(self.p, _ptr(idx), _ptr(off), _ptr(fill), _ptr(x16), _ptr(xp), _ptr(slot),
                                PcScatter(rows, topk, d8))
+
+    def scatter_noalloc(self, idx, off, fill, x16, xp, slot, rows, topk, d8, experts):
+        lib().moe_cuda_scatter_noalloc(self.p, _ptr(idx), _ptr(off), _ptr(fill), _ptr(x16), _ptr(xp), _ptr(slot),
+                                       PcScatter(rows, topk, d8), experts)
 
     def mm(self, A, B, Cout, amax, tiles, m, n, k, sa=NO_SLOT, sb=NO_SLOT, experts_in_B=1):
         lib().moe_cuda_mm(self.p, _ptr(A), _ptr(B), _ptr(Cout), _ptr(amax), _ptr(tiles), PcMm(m, n, k, sa, sb),
