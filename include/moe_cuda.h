@@ -183,6 +183,31 @@ typedef struct moe_cuda_layer_t {
 uint32_t moe_cuda_moe_rows(uint32_t rows, uint32_t topk, uint32_t experts);
 void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
 
+/* ---- expert parallel over the GPUs of one box (no counterpart in the
+ *      reference, which keeps all experts of a layer on one device,
+ *      src/qwen.c:235-246) ------------------------------------------------
+ * One process per GPU.  Rank g owns experts [g*E/G, (g+1)*E/G) and passes only
+ * their weights; every rank passes its own tokens.  Dispatch and return are
+ * fused into the scatter and combine kernels as peer stores / loads over
+ * NVLink; NCCL carries the per-expert counts and two barriers. */
+typedef struct moe_cuda_ep_cfg_t {
+    uint32_t experts, topk, d, inter; /* global expert count; experts % world == 0, inter % 128 == 0 */
+    uint32_t max_rows;                /* most tokens any rank will pass in one call */
+} moe_cuda_ep_cfg_t;
+/* 128 bytes of NCCL unique id: call on one rank, hand the bytes to all. */
+int moe_cuda_ep_unique_id(void *out128);
+/* Rows of each rank's expert-contiguous buffers: sized for the worst case
+ * (every token of every rank routed to this rank), so no token is ever dropped. */
+uint32_t moe_cuda_ep_rows(uint32_t world, uint32_t max_rows, uint32_t experts, uint32_t topk);
+/* Collective: joins the communicator, allocates and cross-maps the buffers. */
+void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, int rank, int world,
+                      const moe_cuda_ep_cfg_t *cfg);
+/* Collective: one MoE layer.  L->rows = this rank's tokens, L->experts = global
+ * expert count, L->wgu / L->wdown = this rank's experts only.  L->slot receives
+ * row numbers inside the owning rank's buffer, L->off this rank's first row per
+ * expert there.  Shared expert, L->tiles and the flags are not supported. */
+void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
+
 /* Per-stage device times of the last moe_cuda_layer call, in milliseconds, in
  * the order route, scan, scatter, gate_up, down, shared, combine (after
  * mda_vkc_prof_begin / prof_report, src/vkc.c:595-653).  Enabled with

@@ -8,4 +8,4 @@ named shapes) and `build` (nvcc / gcc recipes).
 The directory name has a hyphen, so import it through `__graft_entry__.load_package()`,
 which registers it as the module `r_mda_b200`.
 """
-from . import build, moe_cuda, synth  # noqa: F401
+from . import build, ep_plan, moe_cuda, synth  # noqa: F401

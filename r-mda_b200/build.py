@@ -27,7 +27,7 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
     srcs = sorted(glob.glob(os.path.join(PKG, "csrc", "*.cu")))
     deps = srcs + glob.glob(os.path.join(PKG, "csrc", "*.cuh")) + [os.path.join(ROOT, "include", "moe_cuda.h")]
     if force or _stale(LIB, deps):
-        cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + srcs
+        cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + srcs + ["-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)

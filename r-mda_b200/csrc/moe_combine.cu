@@ -28,9 +28,12 @@ moe_combine_kernel(moe_combine_args a) {
     __shared__ float s_wt[MOE_MAX_TOPK];
     __shared__ float s_f[8];
     __shared__ float s_red[CB_THREADS / 32];
+    __shared__ const YT *s_y[MOE_MAX_TOPK];
     uint32_t r = blockIdx.x;
-    const YT *y = reinterpret_cast<const YT *>(a.y);
     if (threadIdx.x < a.topk) {
+        // expert-parallel: the row is read from the GPU that owns its expert, over NVLink
+        s_y[threadIdx.x] = reinterpret_cast<const YT *>(
+            a.y_peers != NULL ? a.y_peers[a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank] : a.y);
         s_slot[threadIdx.x] = a.slot[(size_t)r * a.topk + threadIdx.x];
         s_wt[threadIdx.x] = a.wt[(size_t)r * a.topk + threadIdx.x];
     }
@@ -50,7 +53,7 @@ moe_combine_kernel(moe_combine_args a) {
     for (uint32_t c = threadIdx.x * 4u; c < a.d; c += CB_THREADS * 4u, it += 1) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (uint32_t j = 0; j < a.topk; j += 1) {
-            float4 v = moe_load4(y + (size_t)s_slot[j] * a.d + c);
+            float4 v = moe_load4(s_y[j] + (size_t)s_slot[j] * a.d + c);
             float w = s_wt[j];
             acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
             acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
@@ -114,7 +117,8 @@ moe_combine_kernel(moe_combine_args a) {
 
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a) {
     if (!MOE_LIVE(c)) return;
-    MOE_REQUIRE(c, a.wt != NULL && a.slot != NULL && a.y != NULL, "combine: null buffer");
+    MOE_REQUIRE(c, a.wt != NULL && a.slot != NULL && (a.y != NULL || a.y_peers != NULL), "combine: null buffer");
+    MOE_REQUIRE(c, a.y_peers == NULL || (a.idx != NULL && a.experts_per_rank >= 1), "combine: peer rows need idx");
     MOE_REQUIRE(c, a.h != NULL || a.y16 != NULL, "combine: no output");
     MOE_REQUIRE(c, a.sh == NULL || a.proj != NULL, "combine: shared term needs proj");
     MOE_REQUIRE(c, a.topk >= 1 && a.topk <= MOE_MAX_TOPK, "combine: topk %u outside 1..16", a.topk);

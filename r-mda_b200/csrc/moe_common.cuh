@@ -92,7 +92,8 @@ void moe_launch_scan(moe_cuda_ctx *c, const uint32_t *count, uint32_t *off, uint
                      uint32_t experts, uint32_t tile);
 void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, uint32_t *fill,
                         const void *x16, void *xp, uint32_t *slot, uint32_t rows, uint32_t topk,
-                        uint32_t d8, uint32_t experts_bound);
+                        uint32_t d8, uint32_t experts_bound, void *const *xp_peers = NULL,
+                        uint32_t experts_per_rank = 0);
 
 enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // Grouped product.  mode F32: C fp32 [m x n] = A*B^T * s;  SWIGLU_F16: B holds
@@ -101,7 +102,7 @@ enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // a_rows = rows A really holds (<= m); rows beyond read as zero.
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C,
                    const uint32_t *amax, const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k,
-                   uint32_t sa, uint32_t sb, uint32_t experts_in_B, uint32_t a_rows);
+                   uint32_t sa, uint32_t sb, uint32_t experts_in_B, uint32_t a_rows, bool prefix = false);
 
 struct moe_combine_args {
     const float *wt;
@@ -116,6 +117,10 @@ struct moe_combine_args {
     float eps;
     uint32_t rows, d, topk, pstride, sg_off, inj_stride, inj_off, hc;
     bool y_is_f16;
+    // expert-parallel: row j of a token lives in y_peers[idx[r,j] / experts_per_rank]
+    const uint32_t *idx;
+    const void *const *y_peers;
+    uint32_t experts_per_rank;
 };
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a);
 

@@ -1,4 +1,334 @@
-// Expert-parallel layer: placeholder translation unit until the NCCL path lands.
+// Expert-parallel MoE layer over the GPUs of one box: one process per GPU,
+// experts split contiguously (rank g owns experts [g*E/G, (g+1)*E/G)), tokens
+// stay on their home GPU.  The reference is single-GPU (all experts of a layer
+// live in one buffer, src/qwen.c:235-246); the result here must equal the
+// single-GPU layer's.
+//
+// The two all-to-alls are fused into the kernels on either side of them instead
+// of being library calls:
+//   dispatch: the scatter kernel writes each permuted row straight into the
+//             owning GPU's expert-contiguous buffer (peer stores over NVLink);
+//   return:   the combine kernel gathers each expert output row straight from
+//             the owning GPU's buffer (peer loads over NVLink).
+// Peer buffers are plain cudaMalloc memory mapped with CUDA IPC; all accesses
+// are ordinary ld/st (no multimem, no TMA from peer memory: the grouped
+// products only ever read local HBM).  NCCL carries what is left: the
+// per-expert counts (one all-gather) and two stream-ordered barriers (4-byte
+// all-reduces) that separate "all rows landed" from the products and "all
+// products done" from the combine.
+//
+// Row order inside an expert is (source rank, token index); with contiguous
+// token blocks per rank that is the global token order, so the permutation is
+// the single-GPU one restricted to the expert.
+#include <dlfcn.h>
+#include <nccl.h>
+#include <stdlib.h>
+#include <string.h>
+
 #include "moe_common.cuh"
 
-void moe_ep_teardown(moe_cuda_ctx *c) { (void)c; }
+struct moe_nccl_api {
+    void *handle;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *);
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    ncclResult_t (*CommAbort)(ncclComm_t);
+    const char *(*GetErrorString)(ncclResult_t);
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+};
+
+static moe_nccl_api g_nccl;
+
+static bool moe_nccl_load(char *why, size_t n) {
+    if (g_nccl.handle != NULL) return true;
+    void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);  // reuses a copy the process already loaded
+    if (h == NULL) {
+        snprintf(why, n, "libnccl.so.2 not loadable: %s", dlerror());
+        return false;
+    }
+#define MOE_SYM(field, name)                                  \
+    *(void **)(&g_nccl.field) = dlsym(h, name);               \
+    if (g_nccl.field == NULL) {                               \
+        snprintf(why, n, "libnccl.so.2 lacks %s", name);      \
+        return false;                                         \
+    }
+    MOE_SYM(GetUniqueId, "ncclGetUniqueId")
+    MOE_SYM(CommInitRank, "ncclCommInitRank")
+    MOE_SYM(CommDestroy, "ncclCommDestroy")
+    MOE_SYM(CommAbort, "ncclCommAbort")
+    MOE_SYM(GetErrorString, "ncclGetErrorString")
+    MOE_SYM(AllGather, "ncclAllGather")
+    MOE_SYM(AllReduce, "ncclAllReduce")
+#undef MOE_SYM
+    g_nccl.handle = h;
+    return true;
+}
+
+#define MOE_EP_MAX_WORLD 16
+
+struct moe_ep_state {
+    ncclComm_t comm;
+    int rank, world;
+    moe_cuda_ep_cfg_t cfg;
+    uint32_t el;          // experts per rank
+    uint32_t mcap;        // rows of the local expert-contiguous buffers
+    __half *xp, *ye, *hp16;              // local [mcap x d], [mcap x d], [mcap x inter]
+    void *xp_peer[MOE_EP_MAX_WORLD];     // every rank's xp as mapped here (own entry = local pointer)
+    void *ye_peer[MOE_EP_MAX_WORLD];
+    void **xp_peer_dev, **ye_peer_dev;   // the same tables in device memory
+    uint32_t *cnt_all;                   // [world][experts]
+    uint32_t *dst_off;                   // [experts]: first row of this rank's rows in the owner's buffer
+    uint32_t *tiles;                     // [mcap/128] local tile schedule
+    uint32_t *idx, *slot, *count, *bar;
+    float *wt;
+};
+
+#define MOE_NCCL_TRY(c, expr)                                                                   \
+    do {                                                                                        \
+        ncclResult_t r__ = (expr);                                                              \
+        if (r__ != ncclSuccess) {                                                               \
+            moe_fail((c), MOE_ERR_COMM, "%s:%d: NCCL: %s", __FILE__, __LINE__, g_nccl.GetErrorString(r__)); \
+            return;                                                                             \
+        }                                                                                       \
+    } while (0)
+
+extern "C" int moe_cuda_ep_unique_id(void *out128) {
+    char why[200];
+    if (out128 == NULL || !moe_nccl_load(why, sizeof(why))) return MOE_ERR_COMM;
+    ncclUniqueId id;
+    if (g_nccl.GetUniqueId(&id) != ncclSuccess) return MOE_ERR_COMM;
+    memcpy(out128, &id, sizeof(id));
+    return MOE_OK;
+}
+
+extern "C" uint32_t moe_cuda_ep_rows(uint32_t world, uint32_t max_rows, uint32_t experts, uint32_t topk) {
+    // Worst case one rank can be sent: every token of every rank picks min(topk, E/G) of its experts.
+    if (world == 0 || experts % world != 0) return 0;
+    uint32_t el = experts / world;
+    uint64_t rows = (uint64_t)world * max_rows * (topk < el ? topk : el) + (uint64_t)el * (MOE_TILE - 1u);
+    rows = (rows + MOE_TILE - 1u) / MOE_TILE * MOE_TILE;
+    return rows < (1ull << 31) ? (uint32_t)rows : 0;
+}
+
+void moe_ep_teardown(moe_cuda_ctx *c) {
+    if (c == NULL || c->ep == NULL) return;
+    moe_ep_state *ep = c->ep;
+    if (c->stream != NULL) cudaStreamSynchronize(c->stream);
+    for (int r = 0; r < ep->world; r += 1) {
+        if (r == ep->rank) continue;
+        if (ep->xp_peer[r] != NULL) cudaIpcCloseMemHandle(ep->xp_peer[r]);
+        if (ep->ye_peer[r] != NULL) cudaIpcCloseMemHandle(ep->ye_peer[r]);
+    }
+    void *mine[] = {ep->xp, ep->ye, ep->hp16, ep->xp_peer_dev, ep->ye_peer_dev, ep->cnt_all, ep->dst_off,
+                    ep->tiles, ep->idx, ep->slot, ep->count, ep->bar, ep->wt};
+    for (size_t i = 0; i < sizeof(mine) / sizeof(mine[0]); i += 1) {
+        if (mine[i] != NULL) cudaFree(mine[i]);
+    }
+    if (ep->comm != NULL) {
+        if (c->status == MOE_OK) g_nccl.CommDestroy(ep->comm);
+        else g_nccl.CommAbort(ep->comm);  // a failed rank must not wait for its peers
+    }
+    free(ep);
+    c->ep = NULL;
+}
+
+// Joins the communicator, allocates the peer-visible buffers for the stated
+// maximum shape and maps every peer's buffers.  Collective over all ranks.
+extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, int rank, int world,
+                                 const moe_cuda_ep_cfg_t *cfg) {
+    if (!MOE_LIVE(c)) return;
+    MOE_REQUIRE(c, c->ep == NULL, "ep_init: already initialised");
+    MOE_REQUIRE(c, unique_id128 != NULL && cfg != NULL, "ep_init: null argument");
+    MOE_REQUIRE(c, world >= 1 && world <= MOE_EP_MAX_WORLD && rank >= 0 && rank < world, "ep_init: rank %d of %d", rank, world);
+    MOE_REQUIRE(c, cfg->experts >= 1 && cfg->experts <= MOE_MAX_EXPERTS && cfg->experts % (uint32_t)world == 0,
+                "ep_init: experts %u not divisible by world %d", cfg->experts, world);
+    MOE_REQUIRE(c, cfg->topk >= 1 && cfg->topk <= MOE_MAX_TOPK && cfg->d % 8 == 0 && cfg->inter % 128 == 0 && cfg->max_rows >= 1,
+                "ep_init: bad shape");
+    char why[200];
+    if (!moe_nccl_load(why, sizeof(why))) {
+        moe_fail(c, MOE_ERR_COMM, "%s", why);
+        return;
+    }
+    uint32_t mcap = moe_cuda_ep_rows((uint32_t)world, cfg->max_rows, cfg->experts, cfg->topk);
+    MOE_REQUIRE(c, mcap != 0, "ep_init: buffer rows overflow");
+    moe_ep_state *ep = (moe_ep_state *)calloc(1, sizeof(moe_ep_state));
+    if (ep == NULL) {
+        moe_fail(c, MOE_ERR_NOMEM, "ep_init: host allocation");
+        return;
+    }
+    c->ep = ep;
+    ep->rank = rank;
+    ep->world = world;
+    ep->cfg = *cfg;
+    ep->el = cfg->experts / (uint32_t)world;
+    ep->mcap = mcap;
+    ncclUniqueId id;
+    memcpy(&id, unique_id128, sizeof(id));
+    MOE_NCCL_TRY(c, g_nccl.CommInitRank(&ep->comm, world, id, rank));
+
+    size_t R = cfg->max_rows, K = cfg->topk, E = cfg->experts;
+    ep->xp = (__half *)moe_cuda_alloc(c, (size_t)mcap * cfg->d * 2);
+    ep->ye = (__half *)moe_cuda_alloc(c, (size_t)mcap * cfg->d * 2);
+    ep->hp16 = (__half *)moe_cuda_alloc(c, (size_t)mcap * cfg->inter * 2);
+    ep->xp_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+    ep->ye_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+    ep->cnt_all = (uint32_t *)moe_cuda_alloc(c, (size_t)world * E * 4);
+    ep->dst_off = (uint32_t *)moe_cuda_alloc(c, E * 4);
+    ep->tiles = (uint32_t *)moe_cuda_alloc(c, (size_t)(mcap / MOE_TILE) * 4);
+    ep->idx = (uint32_t *)moe_cuda_alloc(c, R * K * 4);
+    ep->slot = (uint32_t *)moe_cuda_alloc(c, R * K * 4);
+    ep->wt = (float *)moe_cuda_alloc(c, R * K * 4);
+    ep->count = (uint32_t *)moe_cuda_alloc(c, E * 4);
+    ep->bar = (uint32_t *)moe_cuda_alloc(c, 256);
+    if (c->status != MOE_OK) return;
+    MOE_CUDA_TRY(c, cudaMemsetAsync(ep->bar, 0, 256, c->stream));
+
+    // Exchange the IPC handles of xp and ye through the communicator itself.
+    struct Handles {
+        cudaIpcMemHandle_t xp, ye;
+    };
+    Handles mine;
+    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.xp, ep->xp));
+    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.ye, ep->ye));
+    Handles *d_all = (Handles *)moe_cuda_alloc(c, sizeof(Handles) * (size_t)world);
+    if (d_all == NULL) return;
+    MOE_CUDA_TRY(c, cudaMemcpyAsync(d_all + rank, &mine, sizeof(mine), cudaMemcpyHostToDevice, c->stream));
+    MOE_NCCL_TRY(c, g_nccl.AllGather(d_all + rank, d_all, sizeof(Handles), ncclUint8, ep->comm, c->stream));
+    Handles all[MOE_EP_MAX_WORLD];
+    MOE_CUDA_TRY(c, cudaMemcpyAsync(all, d_all, sizeof(Handles) * (size_t)world, cudaMemcpyDeviceToHost, c->stream));
+    MOE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    cudaFree(d_all);
+    for (int r = 0; r < world; r += 1) {
+        if (r == rank) {
+            ep->xp_peer[r] = ep->xp;
+            ep->ye_peer[r] = ep->ye;
+            continue;
+        }
+        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->xp_peer[r], all[r].xp, cudaIpcMemLazyEnablePeerAccess));
+        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->ye_peer[r], all[r].ye, cudaIpcMemLazyEnablePeerAccess));
+    }
+    MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->xp_peer_dev, ep->xp_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
+    MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->ye_peer_dev, ep->ye_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
+    // nobody may write into a peer before every rank has finished mapping
+    MOE_NCCL_TRY(c, g_nccl.AllReduce(ep->bar, ep->bar + 8, 1, ncclUint32, ncclSum, ep->comm, c->stream));
+    MOE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+}
+
+// From all ranks' per-expert counts: where this rank's rows of expert e start in
+// the owner's buffer (dst_off), and the owner-side tile schedule of this rank's
+// own experts.  One block of 512 threads, thread = global expert.
+__global__ void __launch_bounds__(512)
+moe_ep_plan_kernel(const uint32_t *__restrict__ cnt_all, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
+                   uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status) {
+    __shared__ uint32_t incl_s[512];
+    uint32_t e = threadIdx.x;
+    uint32_t tot = 0, before = 0;
+    if (e < experts) {
+        for (uint32_t s = 0; s < world; s += 1) {
+            uint32_t v = cnt_all[s * experts + e];
+            if (s < rank) before += v;
+            tot += v;
+        }
+    }
+    uint32_t p = (tot + MOE_TILE - 1u) / MOE_TILE * MOE_TILE;
+    incl_s[e] = p;
+    __syncthreads();
+    for (uint32_t o = 1; o < 512; o <<= 1) {  // Hillis-Steele over at most 512 entries
+        uint32_t v = e >= o ? incl_s[e - o] : 0;
+        __syncthreads();
+        incl_s[e] += v;
+        __syncthreads();
+    }
+    if (e < experts) {
+        uint32_t owner = e / el;
+        uint32_t owner_start = owner * el;
+        uint32_t base = owner_start > 0 ? incl_s[owner_start - 1] : 0;
+        uint32_t off = incl_s[e] - p - base;  // rows before expert e inside its owner's buffer
+        if (off + p > mcap) {
+            atomicCAS(status, 0u, (uint32_t)MOE_ERR_ARG | (2u << 8));
+        } else {
+            dst_off[e] = off + before;
+            if (owner == rank) {
+                for (uint32_t t = off / MOE_TILE; t < (off + p) / MOE_TILE; t += 1) tiles[t] = e - owner_start;
+            }
+        }
+    }
+}
+
+extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
+    if (!MOE_LIVE(c)) return;
+    moe_ep_state *ep = c->ep;
+    MOE_REQUIRE(c, ep != NULL, "ep_layer: moe_cuda_ep_init has not run");
+    MOE_REQUIRE(c, L != NULL && L->proj != NULL && L->x16 != NULL && L->wgu != NULL && L->wdown != NULL, "ep_layer: null input");
+    MOE_REQUIRE(c, L->h != NULL || L->y16 != NULL, "ep_layer: no output");
+    MOE_REQUIRE(c, L->experts == ep->cfg.experts && L->topk == ep->cfg.topk && L->d == ep->cfg.d && L->inter == ep->cfg.inter,
+                "ep_layer: shape differs from moe_cuda_ep_init");
+    MOE_REQUIRE(c, L->rows <= ep->cfg.max_rows, "ep_layer: rows %u > max_rows %u", L->rows, ep->cfg.max_rows);
+    MOE_REQUIRE(c, L->shared == 0, "ep_layer: the shared expert is not part of the expert-parallel path");
+    MOE_REQUIRE(c, L->hc >= 1, "ep_layer: hc 0");
+    const uint32_t R = L->rows, K = L->topk, E = L->experts, d = L->d, I = L->inter;
+    const uint32_t mcap = ep->mcap;
+    uint32_t *idx = L->idx != NULL ? L->idx : ep->idx;
+    uint32_t *slot = L->slot != NULL ? L->slot : ep->slot;
+    uint32_t *count = L->count != NULL ? L->count : ep->count;
+    float *wt = L->wt != NULL ? L->wt : ep->wt;
+
+    auto mark = [&](int i) {
+        if (c->prof && c->ev_made && c->status == MOE_OK) cudaEventRecord(c->ev[i], c->stream);
+    };
+    mark(0);
+    moe_cuda_fill(c, count, (size_t)E * 4, 0);
+    moe_cuda_fill(c, ep->tiles, (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
+    if (R != 0) moe_launch_route(c, L->proj, idx, wt, count, R, E, K, L->pstride);
+    mark(1);
+    if (!MOE_LIVE(c)) return;
+    // counts of every rank (also orders this layer after every peer's previous combine)
+    MOE_NCCL_TRY(c, g_nccl.AllGather(count, ep->cnt_all, E, ncclUint32, ep->comm, c->stream));
+    moe_ep_plan_kernel<<<1, 512, 0, c->stream>>>(ep->cnt_all, ep->dst_off, ep->tiles, E, (uint32_t)ep->world,
+                                                 (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev);
+    MOE_LAUNCHED(c);
+    if (L->off != NULL) moe_cuda_copy(c, L->off, ep->dst_off, (size_t)E * 4);
+    mark(2);
+    // dispatch fused into the scatter: rows go to their owner's xp
+    if (R != 0) moe_launch_scatter(c, idx, ep->dst_off, NULL, L->x16, ep->xp, slot, R, K, d / 8u, E, ep->xp_peer_dev, ep->el);
+    if (!MOE_LIVE(c)) return;
+    MOE_NCCL_TRY(c, g_nccl.AllReduce(ep->bar, ep->bar + 8, 1, ncclUint32, ncclSum, ep->comm, c->stream));  // all rows landed
+    mark(3);
+    moe_launch_mm(c, MOE_MM_SWIGLU_F16, ep->xp, L->wgu, ep->hp16, NULL, ep->tiles, mcap, 2u * I, d, MDA_PC_NO_SLOT,
+                  MDA_PC_NO_SLOT, ep->el, mcap, true);
+    mark(4);
+    moe_launch_mm(c, MOE_MM_F16, ep->hp16, L->wdown, ep->ye, NULL, ep->tiles, mcap, d, I, MDA_PC_NO_SLOT,
+                  MDA_PC_NO_SLOT, ep->el, mcap, true);
+    mark(5);
+    if (!MOE_LIVE(c)) return;
+    MOE_NCCL_TRY(c, g_nccl.AllReduce(ep->bar, ep->bar + 8, 1, ncclUint32, ncclSum, ep->comm, c->stream));  // all products done
+    mark(6);
+    if (R != 0) {
+        moe_combine_args a = {};
+        a.wt = wt;
+        a.slot = slot;
+        a.y = ep->ye;
+        a.proj = L->proj;
+        a.inj = L->inj;
+        a.h = L->h;
+        a.x16 = (const __half *)L->x16;
+        a.y16 = (__half *)L->y16;
+        a.eps = L->eps;
+        a.rows = R;
+        a.d = d;
+        a.topk = K;
+        a.pstride = L->pstride;
+        a.sg_off = E;
+        a.inj_stride = L->inj_stride;
+        a.inj_off = L->inj_off;
+        a.hc = L->hc;
+        a.y_is_f16 = true;
+        a.idx = idx;
+        a.y_peers = (const void *const *)ep->ye_peer_dev;
+        a.experts_per_rank = ep->el;
+        moe_launch_combine(c, a);  // return all-to-all fused into the gather
+    }
+    mark(7);
+    if (c->prof && c->ev_made && c->status == MOE_OK) c->ev_valid = true;
+}

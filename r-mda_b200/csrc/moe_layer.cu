@@ -116,10 +116,10 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
     mark(c, 3);
     if (!unfused) {
         moe_launch_mm(c, MOE_MM_SWIGLU_F16, b.xp, L->wgu, b.hp16, NULL, tiles, M, 2u * I, d, MDA_PC_NO_SLOT,
-                      MDA_PC_NO_SLOT, E, M);  // :847-877 in one kernel
+                      MDA_PC_NO_SLOT, E, M, true);  // :847-877 in one kernel
         mark(c, 4);
         moe_launch_mm(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, b.hp16, L->wdown, b.ye, NULL, tiles, M, d, I, MDA_PC_NO_SLOT,
-                      MDA_PC_NO_SLOT, E, M);  // :878
+                      MDA_PC_NO_SLOT, E, M, true);  // :878
         mark(c, 5);
         if (S != 0) {
             moe_cuda_fill(c, b.tiles0, (size_t)(Rp / MOE_TILE) * 4, 0);

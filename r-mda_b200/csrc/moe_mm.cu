@@ -144,6 +144,7 @@ struct MmArgs {
     const uint32_t *amax;
     const uint32_t *tiles;
     uint32_t m, n, k, sa, sb, experts_in_B;
+    uint32_t prefix;  // used tiles form a prefix of tiles[]: stop at the first unused one
     uint32_t *status;
 };
 
@@ -217,7 +218,10 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             bool ok = true;
             for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 WorkItem it;
-                if (!mm_work<MODE>(a, w, nt_count, it)) continue;
+                if (!mm_work<MODE>(a, w, nt_count, it)) {
+                    if (a.prefix) break;
+                    continue;
+                }
                 for (uint32_t kb = 0; kb < kblocks; kb += 1) {
                     if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, 1)) {
                         ok = false;
@@ -256,7 +260,10 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             bool ok = true;
             for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 WorkItem it;
-                if (!mm_work<MODE>(a, w, nt_count, it)) continue;
+                if (!mm_work<MODE>(a, w, nt_count, it)) {
+                    if (a.prefix) break;
+                    continue;
+                }
                 uint32_t as = n_item & 1u, aph = (n_item >> 1) & 1u;
                 if (!mbar_wait(smem_u32(&bars->tmem_empty[as]), aph ^ 1u, abort, a.status, 2)) break;
                 tc_fence_after();
@@ -295,7 +302,10 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         uint32_t n_item = 0;
         for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
             WorkItem it;
-            if (!mm_work<MODE>(a, w, nt_count, it)) continue;
+            if (!mm_work<MODE>(a, w, nt_count, it)) {
+                if (a.prefix) break;
+                continue;
+            }
             uint32_t as = n_item & 1u, aph = (n_item >> 1) & 1u;
             if (!mbar_wait(smem_u32(&bars->tmem_full[as]), aph, abort, a.status, 4)) break;
             tc_fence_after();
@@ -379,7 +389,7 @@ void mm_launch(moe_cuda_ctx *c, const CUtensorMap *tmA, const CUtensorMap *tmB, 
 
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C, const uint32_t *amax,
                    const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k, uint32_t sa, uint32_t sb,
-                   uint32_t experts_in_B, uint32_t a_rows) {
+                   uint32_t experts_in_B, uint32_t a_rows, bool prefix) {
     if (!MOE_LIVE(c)) return;
     MOE_REQUIRE(c, A != NULL && B != NULL && C != NULL && tiles != NULL, "mm: null buffer");
     MOE_REQUIRE(c, a_rows >= 1 && a_rows <= m, "mm: a_rows %u outside 1..m", a_rows);
@@ -403,6 +413,7 @@ void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void
     a.sa = sa;
     a.sb = sb;
     a.experts_in_B = experts_in_B;
+    a.prefix = prefix ? 1u : 0u;
     a.status = c->dev_status_dev;
     uint32_t nt = mode == MOE_MM_SWIGLU_F16 ? n / BN : (n + BN - 1) / BN;
     uint64_t total = (uint64_t)(m / BM) * nt;

@@ -68,9 +68,10 @@ __global__ void __launch_bounds__(SC_THREADS)
 moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__restrict__ off,
                          const uint32_t *__restrict__ base, const uint4 *__restrict__ x16,
                          uint4 *__restrict__ xp, uint32_t *__restrict__ slot, uint32_t pairs, uint32_t topk,
-                         uint32_t d8, uint32_t ebound) {
+                         uint32_t d8, uint32_t ebound, uint4 *const *__restrict__ xp_peers, uint32_t experts_per_rank) {
     __shared__ uint32_t s_e[SC_PAIRS];
     __shared__ uint32_t s_slot[SC_PAIRS];
+    __shared__ uint4 *s_dst[SC_PAIRS];
     uint32_t p0 = blockIdx.x * SC_PAIRS;
     uint32_t np = min(SC_PAIRS, pairs - p0);
     if (threadIdx.x < SC_PAIRS) s_e[threadIdx.x] = threadIdx.x < np ? idx[p0 + threadIdx.x] : ~0u;
@@ -82,6 +83,8 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
             for (uint32_t q = 0; q < threadIdx.x; q += 1) rank += s_e[q] == e;
             uint32_t p = off[e] + base[(size_t)blockIdx.x * ebound + e] + rank;
             s_slot[threadIdx.x] = p;
+            // expert-parallel: the row goes straight into the owning GPU's buffer over NVLink
+            s_dst[threadIdx.x] = xp_peers != NULL ? xp_peers[e / experts_per_rank] : xp;
             slot[p0 + threadIdx.x] = p;  // :27
         } else {
             s_slot[threadIdx.x] = ~0u;
@@ -94,7 +97,7 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
         if (p == ~0u) continue;
         uint32_t r = (p0 + q) / topk;  // :20
         const uint4 *src = x16 + (size_t)r * d8;
-        uint4 *dst = xp + (size_t)p * d8;
+        uint4 *dst = s_dst[q] + (size_t)p * d8;
         uint32_t i = lane;
         for (; i + 96u < d8; i += 128u) {  // four 16-byte loads in flight per lane
             uint4 a = __ldg(src + i), b = __ldg(src + i + 32u), c2 = __ldg(src + i + 64u), d2 = __ldg(src + i + 96u);
@@ -108,7 +111,8 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
 }
 
 void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, uint32_t *fill, const void *x16,
-                        void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t ebound) {
+                        void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t ebound,
+                        void *const *xp_peers, uint32_t experts_per_rank) {
     if (!MOE_LIVE(c)) return;
     MOE_REQUIRE(c, idx != NULL && off != NULL && x16 != NULL && xp != NULL && slot != NULL, "scatter: null buffer");
     MOE_REQUIRE(c, topk >= 1 && d8 >= 1 && ebound >= 1 && ebound <= MOE_MAX_EXPERTS, "scatter: bad shape");
@@ -126,7 +130,8 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
     moe_scatter_colscan_kernel<<<(ebound + 31u) / 32u, 1024, 0, c->stream>>>(hist, fill, nblocks, ebound);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp,
-                                                                    slot, pairs, topk, d8, ebound);
+                                                                    slot, pairs, topk, d8, ebound,
+                                                                    (uint4 *const *)xp_peers, experts_per_rank);
     MOE_LAUNCHED(c);
 }
 
@@ -134,7 +139,7 @@ extern "C" void moe_cuda_scatter(moe_cuda_ctx_t *c, const uint32_t *idx, const u
                                  const void *x16, void *xp, uint32_t *slot, struct mda_pc_moe_scatter_t pc) {
     // The push constants carry no expert count (src/pc.h:381-385); the table is
     // sized for the reference's limit of 512.
-    moe_launch_scatter(c, idx, off, fill, x16, xp, slot, pc.rows, pc.topk, pc.d8, MOE_MAX_EXPERTS);
+    moe_launch_scatter(c, idx, off, fill, x16, xp, slot, pc.rows, pc.topk, pc.d8, MOE_MAX_EXPERTS, NULL, 0);
 }
 
 // ---- scatter without any allocation ---------------------------------------
@@ -189,6 +194,6 @@ extern "C" void moe_cuda_scatter_noalloc(moe_cuda_ctx_t *c, const uint32_t *idx,
     moe_scatter_colscan_kernel<<<(experts + 31u) / 32u, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<(uint32_t)nblocks, SC_THREADS, 0, c->stream>>>(
-        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts);
+        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0);
     MOE_LAUNCHED(c);
 }

@@ -56,6 +56,10 @@ class Layer(C.Structure):
     )
 
 
+class EpCfg(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("experts", "topk", "d", "inter", "max_rows")]
+
+
 _lib = None
 
 
@@ -106,6 +110,12 @@ def lib() -> C.CDLL:
         L.moe_cuda_moe_rows.restype = u32
         L.moe_cuda_moe_rows.argtypes = [u32, u32, u32]
         L.moe_cuda_layer.argtypes = [vp, C.POINTER(Layer)]
+        L.moe_cuda_ep_unique_id.restype = C.c_int
+        L.moe_cuda_ep_unique_id.argtypes = [vp]
+        L.moe_cuda_ep_rows.restype = u32
+        L.moe_cuda_ep_rows.argtypes = [u32, u32, u32, u32]
+        L.moe_cuda_ep_init.argtypes = [vp, vp, C.c_int, C.c_int, C.POINTER(EpCfg)]
+        L.moe_cuda_ep_layer.argtypes = [vp, C.POINTER(Layer)]
         L.moe_cuda_prof.argtypes = [vp, C.c_int]
         L.moe_cuda_prof_read.argtypes = [vp, C.POINTER(C.c_float)]
         L.moe_cuda_launches.restype = C.c_uint64
@@ -254,6 +264,19 @@ class Ctx:
             setattr(L, k, _ptr(v) if isinstance(v, DevBuf) or v is None else v)
         lib().moe_cuda_layer(self.p, C.byref(L))
 
+    def ep_init(self, unique_id: bytes, rank: int, world: int, experts, topk, d, inter, max_rows):
+        assert len(unique_id) == 128
+        buf = C.create_string_buffer(unique_id, 128)
+        cfg = EpCfg(experts, topk, d, inter, max_rows)
+        lib().moe_cuda_ep_init(self.p, buf, rank, world, C.byref(cfg))
+        self.check()
+
+    def ep_layer(self, **kw):
+        L = Layer()
+        for k, v in kw.items():
+            setattr(L, k, _ptr(v) if isinstance(v, DevBuf) or v is None else v)
+        lib().moe_cuda_ep_layer(self.p, C.byref(L))
+
     def prof(self, on: bool):
         lib().moe_cuda_prof(self.p, 1 if on else 0)
 
@@ -261,6 +284,14 @@ class Ctx:
         ms = (C.c_float * len(PROF_STAGES))()
         lib().moe_cuda_prof_read(self.p, ms)
         return {n: float(ms[i]) for i, n in enumerate(PROF_STAGES)}
+
+
+def ep_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    rc = lib().moe_cuda_ep_unique_id(buf)
+    if rc != MOE_OK:
+        raise MoeCudaError(rc, "could not create an NCCL unique id")
+    return buf.raw
 
 
 def moe_rows(rows: int, topk: int, experts: int) -> int:

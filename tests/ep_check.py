@@ -1,0 +1,72 @@
+"""Run under torch.distributed.run with one rank per GPU: the expert-parallel layer
+(moe_cuda_ep_layer) against the CPU oracle's single-device layer on the whole batch.
+Prints "EP_CHECK_OK <world>" on rank 0 when every rank agrees."""
+import dataclasses
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+from oracle import moe_oracle as O  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = entry.load_package()
+    mc, synth, epp = pkg.moe_cuda, pkg.synth, pkg.ep_plan
+    ok = True
+    for T_local, E, K, d, I, beta in [(300, 32, 4, 512, 256, 0.0), (1024, 128, 8, 2048, 768, 1.0)]:
+        cfg = dataclasses.replace(synth.CONFIGS["c1"], T=T_local * world, E=E, K=K, d=d, I=I, zipf_beta=beta)
+        inp = synth.layer_inputs(cfg, 7)
+        full = O.layer(inp.proj, inp.x16, inp.wgu, inp.wdown, K)
+        el = E // world
+        lo, hi = rank * T_local, (rank + 1) * T_local
+        uid = [mc.ep_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        with mc.Ctx(local) as ctx:
+            ctx.ep_init(uid[0], rank, world, E, K, d, I, T_local)
+            d_proj, d_x = ctx.upload(np.ascontiguousarray(inp.proj[lo:hi])), ctx.upload(np.ascontiguousarray(inp.x16[lo:hi]))
+            d_wgu = ctx.upload(np.ascontiguousarray(inp.wgu[rank * el:(rank + 1) * el]))
+            d_wdown = ctx.upload(np.ascontiguousarray(inp.wdown[rank * el:(rank + 1) * el]))
+            d_idx, d_slot, d_wt = ctx.alloc(T_local * K * 4), ctx.alloc(T_local * K * 4), ctx.alloc(T_local * K * 4)
+            d_off = ctx.alloc(E * 4)
+            for rep in range(2):    # the second pass reuses the peer buffers
+                d_h = ctx.zeros(T_local * d * 4)
+                ctx.ep_layer(rows=T_local, d=d, experts=E, topk=K, inter=I, shared=0, pstride=cfg.pstride, hc=1,
+                             proj=d_proj, x16=d_x, wgu=d_wgu, wdown=d_wdown, h=d_h, idx=d_idx, slot=d_slot,
+                             wt=d_wt, off=d_off)
+                ctx.flush()
+                idx = d_idx.read(np.uint32, (T_local, K))
+                slot = d_slot.read(np.uint32, (T_local, K))
+                h = d_h.read(np.float32, (T_local, d))
+                # expected rows: single-device slot, rebased from the global to the owner's offsets
+                cnt_all = np.stack([np.bincount(full.idx[r * T_local:(r + 1) * T_local].ravel(), minlength=E)
+                                    for r in range(world)]).astype(np.uint32)
+                off_owner = np.concatenate([epp.plan(cnt_all, o)[1] for o in range(world)])
+                want = full.slot[lo:hi].astype(np.int64) - full.off[idx] + off_owner[idx]
+                err = np.abs(h - full.h[lo:hi, 0])
+                good = (np.array_equal(idx, full.idx[lo:hi]) and np.array_equal(slot, want)
+                        and np.array_equal(d_off.read(np.uint32, (E,)), epp.plan(cnt_all, rank)[0])
+                        and bool(np.all(err <= 1e-3 + 2e-2 * np.abs(full.h[lo:hi, 0]))))
+                if not good:
+                    print(f"rank {rank}: mismatch T{T_local} E{E} rep{rep}: idx {np.array_equal(idx, full.idx[lo:hi])} "
+                          f"slot {np.array_equal(slot, want)} max err {err.max():.3e}", flush=True)
+                ok = ok and good
+            dist.barrier()
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0 and int(flag.item()) == 1:
+        print(f"EP_CHECK_OK {world}", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,59 @@
+"""The C-ABI library loads without a GPU, exports every symbol its header declares, and refuses
+to work (instead of falling back to the CPU) when no sm_100 device is usable."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "moe_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(moe_cuda_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(mc):
+    lib = mc.lib()
+    names = declared_functions()
+    assert len(names) >= 25
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/moe_cuda.h but not exported"
+
+
+def test_push_constant_layouts(mc):
+    # sizes of src/pc.h:369-404 and of the glue structs
+    assert ctypes.sizeof(mc.PcRoute) == 16 and ctypes.sizeof(mc.PcScan) == 8 and ctypes.sizeof(mc.PcScatter) == 12
+    assert ctypes.sizeof(mc.PcMm) == 20 and ctypes.sizeof(mc.PcCombine) == 32
+    assert ctypes.sizeof(mc.PcElem) == 28 and ctypes.sizeof(mc.PcSlot) == 8
+
+
+def test_no_cpu_fallback_without_device(mc):
+    import torch
+    if torch.cuda.is_available():
+        return  # covered by the GPU tests
+    c = mc.Ctx(0)
+    assert c.status() == mc.MOE_ERR_CUDA
+    assert "no usable CUDA device" in c.last_error()
+    assert mc.lib().moe_cuda_alloc(c.p, 64) is None   # every later call is a no-op
+    c.close()
+
+
+def test_moe_rows_formula(mc, oracle):
+    for rows, k, e in [(512, 2, 8), (4096, 8, 128), (16384, 10, 512), (1, 1, 1)]:
+        assert mc.moe_rows(rows, k, e) == oracle.moe_rows(rows, k, e)
+    assert mc.lib().moe_cuda_ep_rows(8, 4096, 128, 8) == (8 * 4096 * 8 + 16 * 127 + 127) // 128 * 128
+
+
+def test_host_mirror_builds(pkg):
+    assert os.path.exists(pkg.build.build_host())
+
+
+def test_product_path_does_not_touch_the_oracle():
+    """Nothing under the package or bench's own arm may import or link the oracle."""
+    pkg_dir = os.path.join(ROOT, "r-mda_b200")
+    for dirpath, _, files in os.walk(pkg_dir):
+        for f in files:
+            if f.endswith((".py", ".c", ".h", ".cu", ".cuh")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "moe_ref" not in text and "moe_oracle" not in text, os.path.join(dirpath, f)
