@@ -182,10 +182,14 @@ def run_ours(args):
     d_wgu, d_wdown = ctx.upload(inp.wgu), ctx.upload(inp.wdown)
     d_wsgu = ctx.upload(inp.wsgu) if cfg.S else None
     d_wsdown = ctx.upload(inp.wsdown) if cfg.S else None
+    if args.flags & mc.LAYER_WEIGHTS_TILED:   # upload-time re-tiling, outside the timed region like the upload itself
+        t_gu, t_dn = ctx.tile_weights(d_wgu, E, 2 * I, d), ctx.tile_weights(d_wdown, E, d, I)
+        d_wgu.free(); d_wdown.free()
+        d_wgu, d_wdown = t_gu, t_dn
     d_proj, d_x = ctx.upload(inp.proj), ctx.upload(inp.x16)
     d_h = ctx.zeros(T * d * 4)
     lay = dict(rows=T, d=d, experts=E, topk=K, inter=I, shared=cfg.S, pstride=cfg.pstride, hc=1,
-               proj=d_proj, x16=d_x, wgu=d_wgu, wdown=d_wdown, wsgu=d_wsgu, wsdown=d_wsdown, h=d_h)
+               proj=d_proj, x16=d_x, wgu=d_wgu, wdown=d_wdown, wsgu=d_wsgu, wsdown=d_wsdown, h=d_h, flags=args.flags)
 
     def step():
         ctx.layer(**lay)
@@ -300,6 +304,7 @@ def main():
     ap.add_argument("--config", default="c1", choices=["c0", "c1", "c2", "c3", "c3b"])
     ap.add_argument("--ref-tokens", type=int, default=1 << 30, help="tokens per CPU sample/step (default: the whole workload)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--flags", type=int, default=0, help="MOE_LAYER_* flags passed to moe_cuda_layer")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -49,6 +49,7 @@ struct moe_cuda_ctx {
     uint64_t launches;
     int fail_alloc_countdown;
     bool mm_attr_set[4];
+    bool sw_attr_set[8];
     moe_ep_state *ep;
 };
 
@@ -102,7 +103,15 @@ enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // a_rows = rows A really holds (<= m); rows beyond read as zero.
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C,
                    const uint32_t *amax, const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k,
-                   uint32_t sa, uint32_t sb, uint32_t experts_in_B, uint32_t a_rows, bool prefix = false);
+                   uint32_t sa, uint32_t sb, uint32_t experts_in_B, uint32_t a_rows, bool prefix = false,
+                   bool tiled = false);
+
+// Weight-stationary grouped product over token chunks (moe_mm_swap.cu).
+void moe_launch_chunks(moe_cuda_ctx *c, const uint32_t *count, const uint32_t *off, uint32_t experts, void *chunks,
+                       uint32_t *n_chunks, uint32_t max_chunks);
+void moe_launch_mm_swap(moe_cuda_ctx *c, int mode, int pair, const void *X, uint32_t rows_x, const void *W,
+                        uint32_t experts_in_W, void *C, uint32_t ldc, const void *chunks, const uint32_t *n_chunks,
+                        uint32_t max_chunks, uint32_t n, uint32_t k);
 
 struct moe_combine_args {
     const float *wt;

@@ -30,7 +30,8 @@ struct Carver {
 };
 
 struct LayerBufs {
-    uint32_t *idx, *slot, *count, *off, *fill, *tiles, *amax, *tiles0;
+    uint32_t *idx, *slot, *count, *off, *fill, *tiles, *amax, *tiles0, *n_chunks;
+    void *chunks;
     float *wt;
     __half *xp, *hp16, *hs16;
     void *ye;
@@ -48,6 +49,8 @@ void carve(Carver &cv, LayerBufs &b, const moe_cuda_layer_t *L, uint32_t M, uint
     b.tiles = (uint32_t *)cv.take((size_t)(M / MOE_TILE) * 4);
     b.amax = (uint32_t *)cv.take(256 * 4);  // MDA_QWEN_MAX_SLOTS, src/qwen.h:13
     b.tiles0 = (uint32_t *)cv.take((size_t)(Rp / MOE_TILE) * 4);
+    b.n_chunks = (uint32_t *)cv.take(64);
+    b.chunks = cv.take((R * K / 256 + E + 1) * 16);
     b.xp = (__half *)cv.take((size_t)M * d * 2);
     b.hp16 = (__half *)cv.take((size_t)M * I * 2);
     b.ye = cv.take((size_t)M * d * ((unfused || ye32) ? 4 : 2));
@@ -114,13 +117,35 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
     mark(c, 2);
     moe_launch_scatter(c, idx, off, unfused ? b.fill : NULL, L->x16, b.xp, slot, R, K, d / 8u, E);  // :822-835
     mark(c, 3);
-    if (!unfused) {
+    if (!unfused && (L->flags & MOE_LAYER_CHUNKED) != 0) {
+        // weight-stationary products over per-expert token chunks (MMA width rounded to 16, not 128)
+        const uint32_t max_chunks = R * K / 256u + E + 1u;
+        int pair1 = ((L->flags & MOE_LAYER_NO_PAIR) == 0 && I % 128u == 0) ? 2 : 1;
+        int pair2 = ((L->flags & MOE_LAYER_NO_PAIR) == 0 && d % 256u == 0) ? 2 : 1;
+        if (d % 128u != 0) pair2 = 0;  // the down product needs whole 128-row weight tiles
+        moe_launch_chunks(c, count, off, E, b.chunks, b.n_chunks, max_chunks);
+        moe_launch_mm_swap(c, MOE_MM_SWIGLU_F16, pair1, b.xp, M, L->wgu, E, b.hp16, I, b.chunks, b.n_chunks, max_chunks,
+                           2u * I, d);  // :847-877 in one kernel
+        mark(c, 4);
+        if (pair2 != 0) {
+            moe_launch_mm_swap(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, pair2, b.hp16, M, L->wdown, E, b.ye, d, b.chunks,
+                               b.n_chunks, max_chunks, d, I);  // :878
+        } else {
+            moe_launch_mm(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, b.hp16, L->wdown, b.ye, NULL, tiles, M, d, I,
+                          MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, E, M, true);
+        }
+        mark(c, 5);
+    }
+    const bool tiled = (L->flags & MOE_LAYER_WEIGHTS_TILED) != 0;
+    if (!unfused && (L->flags & MOE_LAYER_CHUNKED) == 0) {
         moe_launch_mm(c, MOE_MM_SWIGLU_F16, b.xp, L->wgu, b.hp16, NULL, tiles, M, 2u * I, d, MDA_PC_NO_SLOT,
-                      MDA_PC_NO_SLOT, E, M, true);  // :847-877 in one kernel
+                      MDA_PC_NO_SLOT, E, M, true, tiled);  // :847-877 in one kernel
         mark(c, 4);
         moe_launch_mm(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, b.hp16, L->wdown, b.ye, NULL, tiles, M, d, I, MDA_PC_NO_SLOT,
-                      MDA_PC_NO_SLOT, E, M, true);  // :878
+                      MDA_PC_NO_SLOT, E, M, true, tiled);  // :878
         mark(c, 5);
+    }
+    if (!unfused) {
         if (S != 0) {
             moe_cuda_fill(c, b.tiles0, (size_t)(Rp / MOE_TILE) * 4, 0);
             moe_launch_mm(c, MOE_MM_SWIGLU_F16, L->x16, L->wsgu, b.hs16, NULL, b.tiles0, Rp, 2u * S, d, MDA_PC_NO_SLOT,

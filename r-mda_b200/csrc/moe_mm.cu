@@ -17,9 +17,13 @@
 // i.e. shader/qwen_elem.comp op 0 + the fp16 store fused into the product) and
 // F16 (fp16 C).  Every spin on an mbarrier is bounded; on timeout the kernel
 // records MOE_ERR_TIMEOUT in the context's status word and unwinds.
-#include "moe_common.cuh"
+#include <stdlib.h>
+
+#include "moe_tc.cuh"
 
 namespace {
+
+using namespace moe_tc;
 
 constexpr uint32_t BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr uint32_t A_BYTES = BM * BK * 2;       // 16 KB
@@ -27,7 +31,6 @@ constexpr uint32_t BH_BYTES = 128 * BK * 2;     // 16 KB: half of the B tile
 constexpr uint32_t STAGE_BYTES = A_BYTES + 2 * BH_BYTES;
 constexpr uint32_t MM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint64_t WAIT_NS = 2000000000ull;     // bound of any single wait
 
 struct __align__(8) MmBarriers {
     uint64_t full[STAGES];
@@ -39,112 +42,15 @@ struct __align__(8) MmBarriers {
 };
 constexpr uint32_t MM_SMEM = STAGES * STAGE_BYTES + sizeof(MmBarriers) + 1024;
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait.  False = gave up (own timeout, or another role raised abort).
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort, uint32_t *status,
-                                       uint32_t site) {
-    uint32_t spins = 0;
-    uint64_t t0 = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        spins += 1;
-        if ((spins & 0xffu) == 0) {
-            if (*abort != 0) return false;
-            uint64_t now = globaltimer_ns();
-            if (t0 == 0) {
-                t0 = now;
-            } else if (now - t0 > WAIT_NS) {
-                *abort = 1;
-                atomicCAS(status, 0u, (uint32_t)MOE_ERR_TIMEOUT | (site << 8));
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        :
-        : "r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row
-// groups 1024 bytes apart, descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor, kind::f16: D fp32, A/B fp16, both K-major, M 128.
-__device__ __forceinline__ uint32_t umma_idesc(uint32_t n) {
-    return (1u << 4) | ((n >> 3) << 17) | ((BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        :
-        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-
 struct MmArgs {
     void *C;
     const uint32_t *amax;
     const uint32_t *tiles;
     uint32_t m, n, k, sa, sb, experts_in_B;
     uint32_t prefix;  // used tiles form a prefix of tiles[]: stop at the first unused one
+    uint32_t dbg;
+    uint32_t bigbox;  // B tensor map has 256-row boxes: one load per stage instead of two
+    uint32_t tiled;   // B is stored as contiguous 128-row x 64-column blocks (moe_cuda_tile_weights)
     uint32_t *status;
 };
 
@@ -231,8 +137,18 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     uint32_t base = stage0 + s * STAGE_BYTES;
                     mbar_expect_tx(full, A_BYTES + (it.nvalid == BN ? 2 * BH_BYTES : BH_BYTES));
                     tma_load_2d(base, &tmA, full, (int32_t)(kb * BK), (int32_t)(it.mt * BM));
-                    tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
-                    if (it.nvalid == BN) tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb1);
+                    if (a.tiled) {
+                        // block (128 weight rows, 64 columns) number = (row / 128) * kblocks + kb; 16 KB contiguous in HBM
+                        tma_load_2d(base + A_BYTES, &tmB, full, 0, (int32_t)((((uint32_t)it.rb0 >> 7) * kblocks + kb) << 7));
+                        if (it.nvalid == BN) {
+                            tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, 0, (int32_t)((((uint32_t)it.rb1 >> 7) * kblocks + kb) << 7));
+                        }
+                    } else if (a.bigbox) {
+                        tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
+                    } else {
+                        tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
+                        if (it.nvalid == BN) tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb1);
+                    }
                     issued |= 1u << s;
                     last_par = (last_par & ~(1u << s)) | (ph << s);
                     s += 1;
@@ -268,7 +184,7 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 if (!mbar_wait(smem_u32(&bars->tmem_empty[as]), aph ^ 1u, abort, a.status, 2)) break;
                 tc_fence_after();
                 uint32_t tmem_d = tmem_base + as * BN;
-                uint32_t idesc = umma_idesc(it.nvalid);
+                uint32_t idesc = umma_idesc(BM, it.nvalid);
                 for (uint32_t kb = 0; kb < kblocks; kb += 1) {
                     if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort, a.status, 3)) {
                         ok = false;
@@ -277,12 +193,16 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     tc_fence_after();
                     uint32_t base = stage0 + s * STAGE_BYTES;
                     uint64_t ad = umma_desc(base), bd = umma_desc(base + A_BYTES);
+                    if (a.dbg & 8u) {
+                        mbar_arrive(smem_u32(&bars->empty[s]));
+                    } else {
 #pragma unroll
-                    for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
-                        // +32 bytes per K=16 step inside the 128-byte swizzle row
-                        umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
+                            // +32 bytes per K=16 step inside the 128-byte swizzle row
+                            umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        }
+                        umma_commit(smem_u32(&bars->empty[s]));  // frees the stage when these MMAs retire
                     }
-                    umma_commit(smem_u32(&bars->empty[s]));  // frees the stage when these MMAs retire
                     s += 1;
                     if (s == STAGES) {
                         s = 0;
@@ -389,7 +309,7 @@ void mm_launch(moe_cuda_ctx *c, const CUtensorMap *tmA, const CUtensorMap *tmB, 
 
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C, const uint32_t *amax,
                    const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k, uint32_t sa, uint32_t sb,
-                   uint32_t experts_in_B, uint32_t a_rows, bool prefix) {
+                   uint32_t experts_in_B, uint32_t a_rows, bool prefix, bool tiled) {
     if (!MOE_LIVE(c)) return;
     MOE_REQUIRE(c, A != NULL && B != NULL && C != NULL && tiles != NULL, "mm: null buffer");
     MOE_REQUIRE(c, a_rows >= 1 && a_rows <= m, "mm: a_rows %u outside 1..m", a_rows);
@@ -397,11 +317,15 @@ void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void
     MOE_REQUIRE(c, n % 128u == 0 && n >= 128u, "mm: n %u not a multiple of 128", n);
     MOE_REQUIRE(c, mode != MOE_MM_SWIGLU_F16 || n % 256u == 0, "mm: fused SwiGLU needs inter %% 128 == 0 (n = %u)", n);
     MOE_REQUIRE(c, k % 8u == 0 && k >= 8u, "mm: k %u not a multiple of 8", k);
-    MOE_REQUIRE(c, experts_in_B >= 1 && (uint64_t)experts_in_B * n < (1ull << 31), "mm: expert count");
+    MOE_REQUIRE(c, experts_in_B >= 1 && (uint64_t)experts_in_B * n * ((k + BK - 1) / BK) < (1ull << 31), "mm: expert count");
     MOE_REQUIRE(c, (sa == MDA_PC_NO_SLOT && sb == MDA_PC_NO_SLOT) || amax != NULL, "mm: scale slot without amax");
     MOE_REQUIRE(c, ((uintptr_t)C & 15) == 0, "mm: C not 16-byte aligned");
     const CUtensorMap *tmA = moe_tmap_2d_f16(c, A, a_rows, k, 128, BK);
-    const CUtensorMap *tmB = moe_tmap_2d_f16(c, B, (uint64_t)experts_in_B * n, k, 128, BK);
+    const uint32_t kblocks_h = (k + BK - 1) / BK;
+    // one 256-row box per stage when every column tile is a full 256 rows of one expert's matrix
+    const bool bigbox = !tiled && mode != MOE_MM_SWIGLU_F16 && n % 256u == 0 && getenv("MOE_DBG") != NULL && (atoi(getenv("MOE_DBG")) & 4);
+    const CUtensorMap *tmB = tiled ? moe_tmap_2d_f16(c, B, (uint64_t)experts_in_B * n * kblocks_h, BK, 128, BK)
+                                   : moe_tmap_2d_f16(c, B, (uint64_t)experts_in_B * n, k, bigbox ? 256 : 128, BK);
     if (tmA == NULL || tmB == NULL) return;
     MmArgs a;
     a.C = C;
@@ -414,6 +338,9 @@ void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void
     a.sb = sb;
     a.experts_in_B = experts_in_B;
     a.prefix = prefix ? 1u : 0u;
+    a.tiled = tiled ? 1u : 0u;
+    a.bigbox = bigbox ? 1u : 0u;
+    a.dbg = getenv("MOE_DBG") ? (uint32_t)atoi(getenv("MOE_DBG")) : 0u;
     a.status = c->dev_status_dev;
     uint32_t nt = mode == MOE_MM_SWIGLU_F16 ? n / BN : (n + BN - 1) / BN;
     uint64_t total = (uint64_t)(m / BM) * nt;
