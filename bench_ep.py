@@ -15,7 +15,7 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
     import torch
     import torch.distributed as dist
 
-    from bench import METRIC, ClockSampler, peaks, pinned_array, workload_config
+    from bench import METRIC, ClockSampler, emit, peaks, pinned_array, workload_config
 
     T, K, E, d, I = cfg.T, cfg.K, cfg.E, cfg.d, cfg.I
     if cfg.S:
@@ -133,7 +133,7 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
                                 "combine + return": stage_ms["combine"]},
             "stages_note": {"gate_up_TFLOP/s": tf1, "down_TFLOP/s": tf2},
         }
-        print(json.dumps(out))
+        emit(args, out)
     dist.barrier()
     ctx.close()
     dist.destroy_process_group()

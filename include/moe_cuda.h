@@ -88,6 +88,7 @@ void moe_cuda_fill(moe_cuda_ctx_t *c, void *dst, size_t bytes, uint32_t word);  
 void moe_cuda_copy(moe_cuda_ctx_t *c, void *dst, const void *src, size_t bytes);     /* device to device, src/vkc.c:791-801 */
 void moe_cuda_write(moe_cuda_ctx_t *c, void *dst, const void *host_src, size_t bytes); /* enqueued; host_src must stay valid until flush unless pageable (then staged) */
 void moe_cuda_read(moe_cuda_ctx_t *c, void *host_dst, const void *src, size_t bytes);  /* blocking, src/vkc.c:817-826 */
+void moe_cuda_read_async(moe_cuda_ctx_t *c, void *host_dst, const void *src, size_t bytes); /* enqueued; complete after the next flush.  host_dst should be page-locked.  Lets two contexts overlap one step's copies with the other's kernels. */
 void moe_cuda_flush(moe_cuda_ctx_t *c);                                                /* src/vkc.c:655-668 */
 
 /* ---- the five kernels --------------------------------------------------- */

@@ -21,19 +21,20 @@ __device__ __forceinline__ float4 moe_load4(const __half *p) {
 // One block per row (shader/moe_combine.comp:26-40 uses one thread per element).
 // acc = sum_j wt[r,j] * y[slot[r,j], c] in j order with separately rounded
 // multiply and add, as the expression is written in the shader (:32-34).
-template <typename YT, bool NORM>
+template <typename YT, bool NORM, bool PEER>
 __global__ void __launch_bounds__(CB_THREADS)
 moe_combine_kernel(moe_combine_args a) {
     __shared__ uint32_t s_slot[MOE_MAX_TOPK];
     __shared__ float s_wt[MOE_MAX_TOPK];
     __shared__ float s_f[8];
     __shared__ float s_red[CB_THREADS / 32];
-    __shared__ const YT *s_y[MOE_MAX_TOPK];
+    __shared__ const YT *s_y[PEER ? MOE_MAX_TOPK : 1];
     uint32_t r = blockIdx.x;
+    const YT *y = reinterpret_cast<const YT *>(a.y);
     if (threadIdx.x < a.topk) {
-        // expert-parallel: the row is read from the GPU that owns its expert, over NVLink
-        s_y[threadIdx.x] = reinterpret_cast<const YT *>(
-            a.y_peers != NULL ? a.y_peers[a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank] : a.y);
+        if (PEER) {  // expert-parallel: the row is read from the GPU that owns its expert, over NVLink
+            s_y[threadIdx.x] = reinterpret_cast<const YT *>(a.y_peers[a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank]);
+        }
         s_slot[threadIdx.x] = a.slot[(size_t)r * a.topk + threadIdx.x];
         s_wt[threadIdx.x] = a.wt[(size_t)r * a.topk + threadIdx.x];
     }
@@ -53,7 +54,7 @@ moe_combine_kernel(moe_combine_args a) {
     for (uint32_t c = threadIdx.x * 4u; c < a.d; c += CB_THREADS * 4u, it += 1) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (uint32_t j = 0; j < a.topk; j += 1) {
-            float4 v = moe_load4(s_y[j] + (size_t)s_slot[j] * a.d + c);
+            float4 v = moe_load4((PEER ? s_y[j] : y) + (size_t)s_slot[j] * a.d + c);
             float w = s_wt[j];
             acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
             acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
@@ -130,12 +131,16 @@ void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a) {
         MOE_REQUIRE(c, a.x16 != NULL && a.hc == 1 && a.d <= CB_THREADS * 4 * CB_MAXV, "combine: fused norm needs x16, hc 1, d <= 8192");
     }
     if (a.rows == 0) return;
+    const bool peer = a.y_peers != NULL;
+    MOE_REQUIRE(c, !peer || a.y_is_f16, "combine: peer rows are fp16");
     if (a.y16 != NULL) {
-        if (a.y_is_f16) moe_combine_kernel<__half, true><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
-        else moe_combine_kernel<float, true><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
+        if (peer) moe_combine_kernel<__half, true, true><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
+        else if (a.y_is_f16) moe_combine_kernel<__half, true, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
+        else moe_combine_kernel<float, true, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
     } else {
-        if (a.y_is_f16) moe_combine_kernel<__half, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
-        else moe_combine_kernel<float, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
+        if (peer) moe_combine_kernel<__half, false, true><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
+        else if (a.y_is_f16) moe_combine_kernel<__half, false, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
+        else moe_combine_kernel<float, false, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
     }
     MOE_LAUNCHED(c);
 }

@@ -96,6 +96,13 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
                         uint32_t d8, uint32_t experts_bound, void *const *xp_peers = NULL,
                         uint32_t experts_per_rank = 0);
 
+void moe_launch_route_hist(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *wt, uint32_t *hist,
+                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride);
+void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts);
+void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
+                      void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
+                      void *const *xp_peers, uint32_t experts_per_rank);
+
 enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // Grouped product.  mode F32: C fp32 [m x n] = A*B^T * s;  SWIGLU_F16: B holds
 // [gate n/2 rows | up n/2 rows] per expert and C fp16 [m x n/2] = silu(gate)*up;

@@ -240,6 +240,12 @@ extern "C" void moe_cuda_read(moe_cuda_ctx_t *c, void *host_dst, const void *src
     moe_poll_device_status(c);
 }
 
+// Enqueued device-to-host copy; the data is on the host after the next moe_cuda_flush.
+extern "C" void moe_cuda_read_async(moe_cuda_ctx_t *c, void *host_dst, const void *src, size_t bytes) {
+    if (!MOE_LIVE(c)) return;
+    MOE_CUDA_TRY(c, cudaMemcpyAsync(host_dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
+}
+
 extern "C" void moe_cuda_flush(moe_cuda_ctx_t *c) {
     if (c == NULL || c->stream == NULL) return;
     if (c->status == MOE_OK) {

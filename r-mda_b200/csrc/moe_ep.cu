@@ -278,9 +278,15 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         if (c->prof && c->ev_made && c->status == MOE_OK) cudaEventRecord(c->ev[i], c->stream);
     };
     mark(0);
-    moe_cuda_fill(c, count, (size_t)E * 4, 0);
     moe_cuda_fill(c, ep->tiles, (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
-    if (R != 0) moe_launch_route(c, L->proj, idx, wt, count, R, E, K, L->pstride);
+    uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)((R + 7u) / 8u + 1u) * E * 4);
+    if (hist == NULL) return;
+    if (R != 0) {
+        moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride);
+        moe_launch_colscan_counts(c, hist, count, R, E);
+    } else {
+        moe_cuda_fill(c, count, (size_t)E * 4, 0);
+    }
     mark(1);
     if (!MOE_LIVE(c)) return;
     // counts of every rank (also orders this layer after every peer's previous combine)
@@ -291,7 +297,7 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
     if (L->off != NULL) moe_cuda_copy(c, L->off, ep->dst_off, (size_t)E * 4);
     mark(2);
     // dispatch fused into the scatter: rows go to their owner's xp
-    if (R != 0) moe_launch_scatter(c, idx, ep->dst_off, NULL, L->x16, ep->xp, slot, R, K, d / 8u, E, ep->xp_peer_dev, ep->el);
+    if (R != 0) moe_launch_place(c, idx, ep->dst_off, hist, L->x16, ep->xp, slot, R, K, d / 8u, E, ep->xp_peer_dev, ep->el);
     if (!MOE_LIVE(c)) return;
     MOE_NCCL_TRY(c, g_nccl.AllReduce(ep->bar, ep->bar + 8, 1, ncclUint32, ncclSum, ep->comm, c->stream));  // all rows landed
     mark(3);

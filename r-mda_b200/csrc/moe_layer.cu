@@ -104,18 +104,32 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
 
     mark(c, 0);
     // src/qwen.c:793-798
-    moe_cuda_fill(c, count, (size_t)E * 4, 0);
     moe_cuda_fill(c, tiles, (size_t)(M / MOE_TILE) * 4, 0xffffffffu);
     if (unfused) {
+        moe_cuda_fill(c, count, (size_t)E * 4, 0);
         moe_cuda_fill(c, b.fill, (size_t)E * 4, 0);
         moe_cuda_fill(c, b.xp, (size_t)M * d * 2, 0);
         moe_cuda_fill(c, b.amax, 256 * 4, 0);  // mda_qwen_slots_begin, src/qwen.c:500-503
     }
-    moe_launch_route(c, L->proj, idx, wt, count, R, E, K, L->pstride);  // :799-811
-    mark(c, 1);
-    moe_launch_scan(c, count, off, tiles, E, MOE_TILE);  // :812-821
-    mark(c, 2);
-    moe_launch_scatter(c, idx, off, unfused ? b.fill : NULL, L->x16, b.xp, slot, R, K, d / 8u, E);  // :822-835
+    if (unfused) {
+        moe_launch_route(c, L->proj, idx, wt, count, R, E, K, L->pstride);  // :799-811
+        mark(c, 1);
+        moe_launch_scan(c, count, off, tiles, E, MOE_TILE);  // :812-821
+        mark(c, 2);
+        moe_launch_scatter(c, idx, off, b.fill, L->x16, b.xp, slot, R, K, d / 8u, E);  // :822-835
+    } else {
+        // Same results with fewer launches and no contended atomics: the router leaves a
+        // per-8-row expert table, whose column scan gives both count[] and the bases of
+        // the stable ranking.
+        uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)((R + 7u) / 8u) * E * 4);
+        if (hist == NULL) return;
+        moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride);
+        mark(c, 1);
+        moe_launch_colscan_counts(c, hist, count, R, E);
+        moe_launch_scan(c, count, off, tiles, E, MOE_TILE);
+        mark(c, 2);
+        moe_launch_place(c, idx, off, hist, L->x16, b.xp, slot, R, K, d / 8u, E, NULL, 0);
+    }
     mark(c, 3);
     if (!unfused && (L->flags & MOE_LAYER_CHUNKED) != 0) {
         // weight-stationary products over per-expert token chunks (MMA width rounded to 16, not 128)

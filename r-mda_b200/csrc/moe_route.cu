@@ -10,18 +10,30 @@
 #define ROUTE_WARPS 8
 #define ROUTE_SENTINEL -3.0e38f  // shader/moe_route.comp:31
 
+// HIST = false: counts by one atomicAdd per selection, as the shader does (:59).
+// HIST = true (fused layer): block b owns rows [8b, 8b+8) and writes their
+// per-expert pair counts to hist[b][*]; the counts then come out of the scatter's
+// column scan, so no atomic is contended and the block table is ready for the
+// stable ranking.
+// NB = ceil(experts / 128): how many 128-expert blocks each lane really holds.
+template <bool HIST, int NB>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float *__restrict__ proj, uint32_t *__restrict__ idx, float *__restrict__ wt,
                  uint32_t *__restrict__ count, uint32_t rows, uint32_t experts, uint32_t topk,
                  uint32_t stride, uint32_t *status, int vec_ok) {
+    __shared__ uint32_t s_hist[HIST ? MOE_MAX_EXPERTS : 1];
     uint32_t lane = threadIdx.x & 31u;
     uint32_t warp = threadIdx.x >> 5;
     uint32_t nwarps = gridDim.x * ROUTE_WARPS;
+    if (HIST) {
+        for (uint32_t e = threadIdx.x; e < experts; e += ROUTE_WARPS * 32) s_hist[e] = 0;
+        __syncthreads();
+    }
     for (uint32_t r = blockIdx.x * ROUTE_WARPS + warp; r < rows; r += nwarps) {
         const float *row = proj + (size_t)r * stride;
-        float l[16];
+        float l[4 * NB];
 #pragma unroll
-        for (uint32_t j = 0; j < 4; j += 1) {
+        for (uint32_t j = 0; j < NB; j += 1) {
             uint32_t e0 = 4u * lane + 128u * j;
             if (vec_ok && e0 + 3u < experts) {
                 float4 v = __ldg(reinterpret_cast<const float4 *>(row + e0));
@@ -45,7 +57,7 @@ moe_route_kernel(const float *__restrict__ proj, uint32_t *__restrict__ idx, flo
             float lb = ROUTE_SENTINEL;
             uint32_t li = ~0u;
 #pragma unroll
-            for (uint32_t j = 0; j < 16; j += 1) {
+            for (uint32_t j = 0; j < 4 * NB; j += 1) {
                 // ascending expert index inside the lane: q fastest, then the 128-blocks
                 uint32_t e = 4u * lane + 128u * (j >> 2) + (j & 3u);
                 if (((taken >> j) & 1u) == 0u && l[j] > lb) {  // strict >: first of equals (:34)
@@ -87,9 +99,26 @@ moe_route_kernel(const float *__restrict__ proj, uint32_t *__restrict__ idx, flo
         if (lane < topk) {
             idx[(size_t)r * topk + lane] = my_e;
             wt[(size_t)r * topk + lane] = t / z;
-            atomicAdd(&count[my_e], 1u);
+            if (HIST) atomicAdd(&s_hist[my_e], 1u);
+            else atomicAdd(&count[my_e], 1u);
         }
     }
+    if (HIST) {
+        __syncthreads();
+        for (uint32_t e = threadIdx.x; e < experts; e += ROUTE_WARPS * 32) count[(size_t)blockIdx.x * experts + e] = s_hist[e];
+    }
+}
+
+template <bool HIST>
+static void route_dispatch(moe_cuda_ctx *c, uint32_t blocks, const float *proj, uint32_t *idx, float *wt, uint32_t *count,
+                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride, int vec_ok) {
+    const uint32_t nb = (experts + 127u) / 128u;
+    const dim3 g(blocks), t(ROUTE_WARPS * 32);
+    if (nb == 1) moe_route_kernel<HIST, 1><<<g, t, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok);
+    else if (nb == 2) moe_route_kernel<HIST, 2><<<g, t, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok);
+    else if (nb == 3) moe_route_kernel<HIST, 3><<<g, t, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok);
+    else moe_route_kernel<HIST, 4><<<g, t, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok);
+    MOE_LAUNCHED(c);
 }
 
 void moe_launch_route(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *wt, uint32_t *count,
@@ -104,9 +133,22 @@ void moe_launch_route(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *
     uint32_t blocks = (rows + ROUTE_WARPS - 1) / ROUTE_WARPS;
     uint32_t cap = (uint32_t)c->sm_count * 8u;
     if (blocks > cap) blocks = cap;
-    moe_route_kernel<<<blocks, ROUTE_WARPS * 32, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride,
-                                                                 c->dev_status_dev, vec_ok);
-    MOE_LAUNCHED(c);
+    route_dispatch<false>(c, blocks, proj, idx, wt, count, rows, experts, topk, stride, vec_ok);
+}
+
+// Fused-layer front end: routing plus the per-block expert table of the scatter
+// (block = 8 consecutive rows = 8*topk pairs).  hist has ceil(rows/8) x experts words.
+void moe_launch_route_hist(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *wt, uint32_t *hist,
+                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride) {
+    if (!MOE_LIVE(c)) return;
+    MOE_REQUIRE(c, experts >= 1 && experts <= MOE_MAX_EXPERTS, "route: experts %u outside 1..512", experts);
+    MOE_REQUIRE(c, topk >= 1 && topk <= MOE_MAX_TOPK && topk <= experts, "route: topk %u outside 1..min(16, experts)", topk);
+    MOE_REQUIRE(c, stride >= experts, "route: stride %u < experts %u", stride, experts);
+    MOE_REQUIRE(c, proj != NULL && idx != NULL && wt != NULL && hist != NULL, "route: null buffer");
+    if (rows == 0) return;
+    int vec_ok = ((uintptr_t)proj % 16 == 0) && (stride % 4 == 0);
+    uint32_t blocks = (rows + ROUTE_WARPS - 1) / ROUTE_WARPS;  // exactly one block per 8 rows: no grid stride
+    route_dispatch<true>(c, blocks, proj, idx, wt, hist, rows, experts, topk, stride, vec_ok);
 }
 
 extern "C" void moe_cuda_route(moe_cuda_ctx_t *c, const float *proj, uint32_t *idx, float *wt, uint32_t *count,

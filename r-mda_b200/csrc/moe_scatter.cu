@@ -13,6 +13,7 @@
 #include "moe_common.cuh"
 
 #define SC_PAIRS 64u    // pairs per block
+#define SC_MAX_PAIRS 128u
 #define SC_THREADS 256u
 
 __global__ void __launch_bounds__(SC_PAIRS)
@@ -35,19 +36,30 @@ moe_scatter_hist_kernel(const uint32_t *__restrict__ idx, uint32_t *__restrict__
 }
 
 // One block per 32 experts; thread (seg, el) sums a contiguous segment of block
-// rows for expert el, the 32 segment sums are scanned, then each thread rewrites
-// its segment as exclusive prefixes.  fill[e] receives the expert's total.
+// rows for expert el (loads coalesced across el and unrolled so that they
+// overlap), the 32 segment sums are scanned, then each thread rewrites its
+// segment as exclusive prefixes.  fill[e] grows by the expert's total;
+// count_out[e] receives it.
+#define CS_EXPERTS 32u
 __global__ void __launch_bounds__(1024)
 moe_scatter_colscan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fill, uint32_t nblocks,
-                           uint32_t ebound) {
+                           uint32_t ebound, uint32_t *__restrict__ count_out) {
     __shared__ uint32_t seg_sum[32][33];
     uint32_t el = threadIdx.x & 31u, seg = threadIdx.x >> 5;
     uint32_t e = blockIdx.x * 32u + el;
     uint32_t per = (nblocks + 31u) / 32u;
-    uint32_t b0 = seg * per, b1 = min(b0 + per, nblocks);
+    uint32_t b0 = min(seg * per, nblocks), b1 = min(b0 + per, nblocks);
     uint32_t s = 0;
     if (e < ebound) {
-        for (uint32_t b = b0; b < b1; b += 1) s += hist[(size_t)b * ebound + e];
+        uint32_t b = b0;
+        for (; b + 8u <= b1; b += 8u) {
+            uint32_t v[8];
+#pragma unroll
+            for (uint32_t i = 0; i < 8; i += 1) v[i] = hist[(size_t)(b + i) * ebound + e];
+#pragma unroll
+            for (uint32_t i = 0; i < 8; i += 1) s += v[i];
+        }
+        for (; b < b1; b += 1) s += hist[(size_t)b * ebound + e];
     }
     seg_sum[seg][el] = s;
     __syncthreads();
@@ -55,12 +67,26 @@ moe_scatter_colscan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ f
     for (uint32_t q = 0; q < seg; q += 1) base += seg_sum[q][el];
     if (e < ebound) {
         uint32_t run = base;
-        for (uint32_t b = b0; b < b1; b += 1) {
+        uint32_t b = b0;
+        for (; b + 8u <= b1; b += 8u) {
+            uint32_t v[8];
+#pragma unroll
+            for (uint32_t i = 0; i < 8; i += 1) v[i] = hist[(size_t)(b + i) * ebound + e];
+#pragma unroll
+            for (uint32_t i = 0; i < 8; i += 1) {
+                hist[(size_t)(b + i) * ebound + e] = run;
+                run += v[i];
+            }
+        }
+        for (; b < b1; b += 1) {
             uint32_t v = hist[(size_t)b * ebound + e];
             hist[(size_t)b * ebound + e] = run;
             run += v;
         }
-        if (seg == 31 && fill != NULL) fill[e] += run;  // state after the shader's atomics (:25)
+        if (seg == 31) {
+            if (fill != NULL) fill[e] += run;          // state after the shader's atomics (:25)
+            if (count_out != NULL) count_out[e] = run;  // per-expert totals double as the router's counts
+        }
     }
 }
 
@@ -68,13 +94,15 @@ __global__ void __launch_bounds__(SC_THREADS)
 moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__restrict__ off,
                          const uint32_t *__restrict__ base, const uint4 *__restrict__ x16,
                          uint4 *__restrict__ xp, uint32_t *__restrict__ slot, uint32_t pairs, uint32_t topk,
-                         uint32_t d8, uint32_t ebound, uint4 *const *__restrict__ xp_peers, uint32_t experts_per_rank) {
-    __shared__ uint32_t s_e[SC_PAIRS];
-    __shared__ uint32_t s_slot[SC_PAIRS];
-    __shared__ uint4 *s_dst[SC_PAIRS];
-    uint32_t p0 = blockIdx.x * SC_PAIRS;
-    uint32_t np = min(SC_PAIRS, pairs - p0);
-    if (threadIdx.x < SC_PAIRS) s_e[threadIdx.x] = threadIdx.x < np ? idx[p0 + threadIdx.x] : ~0u;
+                         uint32_t d8, uint32_t ebound, uint4 *const *__restrict__ xp_peers, uint32_t experts_per_rank,
+                         uint32_t ppb) {
+    // ppb = pairs per block (<= SC_MAX_PAIRS): 64 in the stand-alone scatter, 8*topk behind the fused router
+    __shared__ uint32_t s_e[SC_MAX_PAIRS];
+    __shared__ uint32_t s_slot[SC_MAX_PAIRS];
+    __shared__ uint4 *s_dst[SC_MAX_PAIRS];
+    uint32_t p0 = blockIdx.x * ppb;
+    uint32_t np = min(ppb, pairs - p0);
+    if (threadIdx.x < SC_MAX_PAIRS) s_e[threadIdx.x] = threadIdx.x < np ? idx[p0 + threadIdx.x] : ~0u;
     __syncthreads();
     if (threadIdx.x < np) {
         uint32_t e = s_e[threadIdx.x];
@@ -127,11 +155,35 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
     moe_scatter_hist_kernel<<<nblocks, SC_PAIRS, ebound * sizeof(uint32_t), c->stream>>>(idx, hist, pairs, ebound,
                                                                                          c->dev_status_dev);
     MOE_LAUNCHED(c);
-    moe_scatter_colscan_kernel<<<(ebound + 31u) / 32u, 1024, 0, c->stream>>>(hist, fill, nblocks, ebound);
+    moe_scatter_colscan_kernel<<<(ebound + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, fill, nblocks, ebound, NULL);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp,
                                                                     slot, pairs, topk, d8, ebound,
-                                                                    (uint4 *const *)xp_peers, experts_per_rank);
+                                                                    (uint4 *const *)xp_peers, experts_per_rank, SC_PAIRS);
+    MOE_LAUNCHED(c);
+}
+
+// Fused front end, after the router wrote the per-8-row tables into `hist`:
+// column scan in place (block bases for the ranking) which also yields count[].
+void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts) {
+    if (!MOE_LIVE(c)) return;
+    if (rows == 0) return;
+    uint32_t nblocks = (rows + 7u) / 8u;
+    moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, NULL, nblocks, experts, count);
+    MOE_LAUNCHED(c);
+}
+
+// Ranking + row copies for blocks of 8 rows (8*topk pairs), bases from `hist`.
+void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
+                      void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
+                      void *const *xp_peers, uint32_t experts_per_rank) {
+    if (!MOE_LIVE(c)) return;
+    if (rows == 0) return;
+    MOE_REQUIRE(c, ((uintptr_t)x16 & 15) == 0 && ((uintptr_t)xp & 15) == 0, "scatter: rows not 16-byte aligned");
+    uint32_t nblocks = (rows + 7u) / 8u;
+    moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp, slot,
+                                                                    rows * topk, topk, d8, experts,
+                                                                    (uint4 *const *)xp_peers, experts_per_rank, 8u * topk);
     MOE_LAUNCHED(c);
 }
 
@@ -191,9 +243,9 @@ extern "C" void moe_cuda_scatter_noalloc(moe_cuda_ctx_t *c, const uint32_t *idx,
     moe_scatter_hist_kernel<<<(uint32_t)nblocks, SC_PAIRS, experts * sizeof(uint32_t), c->stream>>>(
         idx, table, (uint32_t)pairs, experts, c->dev_status_dev);
     MOE_LAUNCHED(c);
-    moe_scatter_colscan_kernel<<<(experts + 31u) / 32u, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts);
+    moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts, NULL);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<(uint32_t)nblocks, SC_THREADS, 0, c->stream>>>(
-        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0);
+        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0, SC_PAIRS);
     MOE_LAUNCHED(c);
 }

@@ -97,6 +97,7 @@ def lib() -> C.CDLL:
         L.moe_cuda_copy.argtypes = [vp, vp, vp, sz]
         L.moe_cuda_write.argtypes = [vp, vp, vp, sz]
         L.moe_cuda_read.argtypes = [vp, vp, vp, sz]
+        L.moe_cuda_read_async.argtypes = [vp, vp, vp, sz]
         L.moe_cuda_flush.argtypes = [vp]
         L.moe_cuda_route.argtypes = [vp, vp, vp, vp, vp, PcRoute]
         L.moe_cuda_scan.argtypes = [vp, vp, vp, vp, PcScan]
