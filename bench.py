@@ -186,10 +186,6 @@ def run_ours(args):
     d_wgu, d_wdown = ctx.upload(inp.wgu), ctx.upload(inp.wdown)
     d_wsgu = ctx.upload(inp.wsgu) if cfg.S else None
     d_wsdown = ctx.upload(inp.wsdown) if cfg.S else None
-    if args.flags & mc.LAYER_WEIGHTS_TILED:   # upload-time re-tiling, outside the timed region like the upload itself
-        t_gu, t_dn = ctx.tile_weights(d_wgu, E, 2 * I, d), ctx.tile_weights(d_wdown, E, d, I)
-        d_wgu.free(); d_wdown.free()
-        d_wgu, d_wdown = t_gu, t_dn
     d_proj, d_x = ctx.upload(inp.proj), ctx.upload(inp.x16)
     d_h = ctx.zeros(T * d * 4)
     lay = dict(rows=T, d=d, experts=E, topk=K, inter=I, shared=cfg.S, pstride=cfg.pstride, hc=1,

@@ -180,16 +180,8 @@ typedef struct moe_cuda_layer_t {
 #define MOE_LAYER_UNFUSED 1u /* run the reference's kernel sequence step by step (fp32 g, absmax rescale) */
 #define MOE_LAYER_YE_F32 2u  /* keep expert outputs fp32 between the down product and the combine */
 #define MOE_LAYER_CHUNKED 4u /* experimental: weight-stationary products over per-expert token chunks (MMA width rounded to 16) instead of the reference's 128-row tile schedule */
-#define MOE_LAYER_WEIGHTS_TILED 16u /* wgu / wdown (and wsgu / wsdown) were rewritten by moe_cuda_tile_weights */
+#define MOE_LAYER_MATERIALIZE_XP 16u /* write the permuted activations xp to HBM as the reference does, instead of letting the gate_up product gather the rows of x16 itself */
 #define MOE_LAYER_NO_PAIR 8u /* with MOE_LAYER_CHUNKED: one CTA per tile instead of tcgen05 cta_group::2 pairs */
-
-/* Weight upload step (the reference converts bf16 -> fp16 on the device right
- * after each layer's upload, src/qwen.c:380-394): rewrites [experts][n x k]
- * row-major fp16 weights as contiguous 128-row x 64-column blocks, which stream
- * from HBM at full rate.  n % 128 == 0, k % 8 == 0; dst holds
- * moe_cuda_tiled_bytes(experts, n, k) bytes and must not alias src. */
-size_t moe_cuda_tiled_bytes(uint32_t experts, uint32_t n, uint32_t k);
-void moe_cuda_tile_weights(moe_cuda_ctx_t *c, const void *src, void *dst, uint32_t experts, uint32_t n, uint32_t k);
 
 /* Rows of scratch the layer needs: round128(rows*topk + experts*127), src/qwen.c:68-70. */
 uint32_t moe_cuda_moe_rows(uint32_t rows, uint32_t topk, uint32_t experts);

@@ -101,17 +101,18 @@ void moe_launch_route_hist(moe_cuda_ctx *c, const float *proj, uint32_t *idx, fl
 void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts);
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
-                      void *const *xp_peers, uint32_t experts_per_rank);
+                      void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row = NULL);
 
 enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // Grouped product.  mode F32: C fp32 [m x n] = A*B^T * s;  SWIGLU_F16: B holds
 // [gate n/2 rows | up n/2 rows] per expert and C fp16 [m x n/2] = silu(gate)*up;
 // F16: C fp16 [m x n].
-// a_rows = rows A really holds (<= m); rows beyond read as zero.
+// a_rows = rows A really holds (<= m); rows beyond read as zero.  With src_row (SWIGLU_F16 only)
+// A is the un-permuted activation matrix [a_rows x k] and tile row p is its row src_row[p].
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C,
                    const uint32_t *amax, const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k,
                    uint32_t sa, uint32_t sb, uint32_t experts_in_B, uint32_t a_rows, bool prefix = false,
-                   bool tiled = false);
+                   const uint32_t *src_row = NULL);
 
 // Weight-stationary grouped product over token chunks (moe_mm_swap.cu).
 void moe_launch_chunks(moe_cuda_ctx *c, const uint32_t *count, const uint32_t *off, uint32_t experts, void *chunks,

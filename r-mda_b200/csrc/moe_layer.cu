@@ -30,7 +30,7 @@ struct Carver {
 };
 
 struct LayerBufs {
-    uint32_t *idx, *slot, *count, *off, *fill, *tiles, *amax, *tiles0, *n_chunks;
+    uint32_t *idx, *slot, *count, *off, *fill, *tiles, *amax, *tiles0, *n_chunks, *src_row;
     void *chunks;
     float *wt;
     __half *xp, *hp16, *hs16;
@@ -50,6 +50,7 @@ void carve(Carver &cv, LayerBufs &b, const moe_cuda_layer_t *L, uint32_t M, uint
     b.amax = (uint32_t *)cv.take(256 * 4);  // MDA_QWEN_MAX_SLOTS, src/qwen.h:13
     b.tiles0 = (uint32_t *)cv.take((size_t)(Rp / MOE_TILE) * 4);
     b.n_chunks = (uint32_t *)cv.take(64);
+    b.src_row = (uint32_t *)cv.take((size_t)M * 4);
     b.chunks = cv.take((R * K / 256 + E + 1) * 16);
     b.xp = (__half *)cv.take((size_t)M * d * 2);
     b.hp16 = (__half *)cv.take((size_t)M * I * 2);
@@ -87,6 +88,8 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
     // The fused SwiGLU epilogue pairs 128 gate columns with 128 up columns.
     const bool unfused = (L->flags & MOE_LAYER_UNFUSED) != 0 || I % 128u != 0 || (S != 0 && S % 128u != 0);
     const bool ye32 = unfused || (L->flags & MOE_LAYER_YE_F32) != 0;
+    // default: no permuted copy of the activations; MOE_LAYER_MATERIALIZE_XP keeps the reference's xp
+    const bool gather = !unfused && (L->flags & (MOE_LAYER_CHUNKED | MOE_LAYER_MATERIALIZE_XP)) == 0;
 
     Carver measure = {NULL, 0};
     LayerBufs b;
@@ -128,7 +131,8 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
         moe_launch_colscan_counts(c, hist, count, R, E);
         moe_launch_scan(c, count, off, tiles, E, MOE_TILE);
         mark(c, 2);
-        moe_launch_place(c, idx, off, hist, L->x16, b.xp, slot, R, K, d / 8u, E, NULL, 0);
+        if (gather) moe_cuda_fill(c, b.src_row, (size_t)M * 4, 0xffffffffu);  // padding rows read as zero
+        moe_launch_place(c, idx, off, hist, L->x16, b.xp, slot, R, K, d / 8u, E, NULL, 0, gather ? b.src_row : NULL);
     }
     mark(c, 3);
     if (!unfused && (L->flags & MOE_LAYER_CHUNKED) != 0) {
@@ -150,13 +154,17 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
         }
         mark(c, 5);
     }
-    const bool tiled = (L->flags & MOE_LAYER_WEIGHTS_TILED) != 0;
     if (!unfused && (L->flags & MOE_LAYER_CHUNKED) == 0) {
-        moe_launch_mm(c, MOE_MM_SWIGLU_F16, b.xp, L->wgu, b.hp16, NULL, tiles, M, 2u * I, d, MDA_PC_NO_SLOT,
-                      MDA_PC_NO_SLOT, E, M, true, tiled);  // :847-877 in one kernel
+        if (gather) {  // the gate_up product fetches the rows of x16 itself; xp is never written
+            moe_launch_mm(c, MOE_MM_SWIGLU_F16, L->x16, L->wgu, b.hp16, NULL, tiles, M, 2u * I, d, MDA_PC_NO_SLOT,
+                          MDA_PC_NO_SLOT, E, R, true, b.src_row);  // :822-877 in one kernel
+        } else {
+            moe_launch_mm(c, MOE_MM_SWIGLU_F16, b.xp, L->wgu, b.hp16, NULL, tiles, M, 2u * I, d, MDA_PC_NO_SLOT,
+                          MDA_PC_NO_SLOT, E, M, true);  // :847-877 in one kernel
+        }
         mark(c, 4);
         moe_launch_mm(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, b.hp16, L->wdown, b.ye, NULL, tiles, M, d, I, MDA_PC_NO_SLOT,
-                      MDA_PC_NO_SLOT, E, M, true, tiled);  // :878
+                      MDA_PC_NO_SLOT, E, M, true);  // :878
         mark(c, 5);
     }
     if (!unfused) {

@@ -17,8 +17,6 @@
 // i.e. shader/qwen_elem.comp op 0 + the fp16 store fused into the product) and
 // F16 (fp16 C).  Every spin on an mbarrier is bounded; on timeout the kernel
 // records MOE_ERR_TIMEOUT in the context's status word and unwinds.
-#include <stdlib.h>
-
 #include "moe_tc.cuh"
 
 namespace {
@@ -48,9 +46,10 @@ struct MmArgs {
     const uint32_t *tiles;
     uint32_t m, n, k, sa, sb, experts_in_B;
     uint32_t prefix;  // used tiles form a prefix of tiles[]: stop at the first unused one
-    uint32_t dbg;
-    uint32_t bigbox;  // B tensor map has 256-row boxes: one load per stage instead of two
-    uint32_t tiled;   // B is stored as contiguous 128-row x 64-column blocks (moe_cuda_tile_weights)
+    // row gather (fused layer): A row p is row src_row[p] of X (~0: padding row, reads as zero)
+    const uint32_t *src_row;
+    const __half *X;
+    uint32_t ldx;
     uint32_t *status;
 };
 
@@ -78,8 +77,12 @@ __device__ __forceinline__ bool mm_work(const MmArgs &a, uint32_t w, uint32_t nt
     return true;
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(MM_THREADS, 1)
+// GATHER: four extra warps (6..9) fill the A tile themselves -- 16-byte async
+// copies of rows of X picked by src_row[], written with the same 128-byte
+// swizzle TMA would apply -- so the permuted copy of the activations never has
+// to exist in HBM.  The weights still arrive by TMA from warp 0.
+template <int MODE, bool GATHER>
+__global__ void __launch_bounds__(MM_THREADS + (GATHER ? 128 : 0), 1)
 moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, MmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -94,7 +97,7 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; s += 1) {
-            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->full[s]), GATHER ? 129 : 1);  // TMA thread + every gather thread
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (uint32_t s = 0; s < 2; s += 1) {
@@ -135,20 +138,10 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     }
                     uint32_t full = smem_u32(&bars->full[s]);
                     uint32_t base = stage0 + s * STAGE_BYTES;
-                    mbar_expect_tx(full, A_BYTES + (it.nvalid == BN ? 2 * BH_BYTES : BH_BYTES));
-                    tma_load_2d(base, &tmA, full, (int32_t)(kb * BK), (int32_t)(it.mt * BM));
-                    if (a.tiled) {
-                        // block (128 weight rows, 64 columns) number = (row / 128) * kblocks + kb; 16 KB contiguous in HBM
-                        tma_load_2d(base + A_BYTES, &tmB, full, 0, (int32_t)((((uint32_t)it.rb0 >> 7) * kblocks + kb) << 7));
-                        if (it.nvalid == BN) {
-                            tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, 0, (int32_t)((((uint32_t)it.rb1 >> 7) * kblocks + kb) << 7));
-                        }
-                    } else if (a.bigbox) {
-                        tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
-                    } else {
-                        tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
-                        if (it.nvalid == BN) tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb1);
-                    }
+                    mbar_expect_tx(full, (GATHER ? 0u : A_BYTES) + (it.nvalid == BN ? 2 * BH_BYTES : BH_BYTES));
+                    if (!GATHER) tma_load_2d(base, &tmA, full, (int32_t)(kb * BK), (int32_t)(it.mt * BM));
+                    tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
+                    if (it.nvalid == BN) tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb1);
                     issued |= 1u << s;
                     last_par = (last_par & ~(1u << s)) | (ph << s);
                     s += 1;
@@ -190,19 +183,17 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                         ok = false;
                         break;
                     }
+                    // gathered rows were written through the generic proxy; the tensor core reads through the async one
+                    if (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     tc_fence_after();
                     uint32_t base = stage0 + s * STAGE_BYTES;
                     uint64_t ad = umma_desc(base), bd = umma_desc(base + A_BYTES);
-                    if (a.dbg & 8u) {
-                        mbar_arrive(smem_u32(&bars->empty[s]));
-                    } else {
 #pragma unroll
-                        for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
-                            // +32 bytes per K=16 step inside the 128-byte swizzle row
-                            umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-                        }
-                        umma_commit(smem_u32(&bars->empty[s]));  // frees the stage when these MMAs retire
+                    for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
+                        // +32 bytes per K=16 step inside the 128-byte swizzle row
+                        umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
+                    umma_commit(smem_u32(&bars->empty[s]));  // frees the stage when these MMAs retire
                     s += 1;
                     if (s == STAGES) {
                         s = 0;
@@ -214,6 +205,56 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             }
         }
         __syncwarp();
+    } else if (GATHER && warp >= 6) {
+        // ---------------- row gather (warps 6..9) ----------------
+        // Thread g of the 128 handles 16-byte chunk (g & 7) of rows (g >> 3) + 16 j, j < 8: eight
+        // consecutive lanes fetch one whole 128-byte line of a row, so every request is a full line.
+        const uint32_t g = (warp - 6u) * 32u + lane;
+        const uint32_t sub = g >> 3, ch = g & 7u;
+        const uint32_t dst_off = sub * 128u + ((ch ^ (sub & 7u)) << 4);  // 128-byte swizzle: chunk ^ (row % 8)
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
+            WorkItem it;
+            if (!mm_work<MODE>(a, w, nt_count, it)) {
+                if (a.prefix) break;
+                continue;
+            }
+            const __half *rowp[8];
+            uint32_t live = 0;
+#pragma unroll
+            for (uint32_t j = 0; j < 8; j += 1) {
+                const uint32_t src = a.src_row[it.mt * BM + j * 16u + sub];
+                rowp[j] = a.X + (size_t)(src == ~0u ? 0u : src) * a.ldx + ch * 8u;
+                live |= (src != ~0u ? 1u : 0u) << j;
+            }
+            for (uint32_t kb = 0; kb < kblocks; kb += 1) {
+                uint32_t got = 1;
+                if (lane == 0) got = mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, 5) ? 1u : 0u;
+                got = __shfl_sync(0xffffffffu, got, 0);
+                if (!got) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t dst = stage0 + s * STAGE_BYTES + dst_off;
+                const uint32_t col = kb * BK + ch * 8u;
+#pragma unroll
+                for (uint32_t j = 0; j < 8; j += 1) {
+                    const uint32_t nbytes = (((live >> j) & 1u) != 0u && col < a.k) ? 16u : 0u;  // 0: zero-filled
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + j * 16u * 128u),
+                                 "l"(rowp[j] + (nbytes != 0u ? kb * BK : 0u)), "r"(nbytes)
+                                 : "memory");
+                }
+                // the hardware arrives on the stage's barrier once this thread's copies have landed
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars->full[s])) : "memory");
+                s += 1;
+                if (s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this thread is in flight when it leaves
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
         const uint32_t q = warp & 3u;  // TMEM lane quarter this warp may read
@@ -295,13 +336,14 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     }
 }
 
-template <int MODE>
+template <int MODE, bool GATHER>
 void mm_launch(moe_cuda_ctx *c, const CUtensorMap *tmA, const CUtensorMap *tmB, const MmArgs &a, uint32_t grid) {
-    if (!c->mm_attr_set[MODE]) {
-        MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_mm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM));
-        c->mm_attr_set[MODE] = true;
+    const int slot = GATHER ? 3 : MODE;
+    if (!c->mm_attr_set[slot]) {
+        MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_mm_kernel<MODE, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM));
+        c->mm_attr_set[slot] = true;
     }
-    moe_mm_kernel<MODE><<<grid, MM_THREADS, MM_SMEM, c->stream>>>(*tmA, *tmB, a);
+    moe_mm_kernel<MODE, GATHER><<<grid, MM_THREADS + (GATHER ? 128 : 0), MM_SMEM, c->stream>>>(*tmA, *tmB, a);
     MOE_LAUNCHED(c);
 }
 
@@ -309,7 +351,7 @@ void mm_launch(moe_cuda_ctx *c, const CUtensorMap *tmA, const CUtensorMap *tmB, 
 
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C, const uint32_t *amax,
                    const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k, uint32_t sa, uint32_t sb,
-                   uint32_t experts_in_B, uint32_t a_rows, bool prefix, bool tiled) {
+                   uint32_t experts_in_B, uint32_t a_rows, bool prefix, const uint32_t *src_row) {
     if (!MOE_LIVE(c)) return;
     MOE_REQUIRE(c, A != NULL && B != NULL && C != NULL && tiles != NULL, "mm: null buffer");
     MOE_REQUIRE(c, a_rows >= 1 && a_rows <= m, "mm: a_rows %u outside 1..m", a_rows);
@@ -317,15 +359,12 @@ void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void
     MOE_REQUIRE(c, n % 128u == 0 && n >= 128u, "mm: n %u not a multiple of 128", n);
     MOE_REQUIRE(c, mode != MOE_MM_SWIGLU_F16 || n % 256u == 0, "mm: fused SwiGLU needs inter %% 128 == 0 (n = %u)", n);
     MOE_REQUIRE(c, k % 8u == 0 && k >= 8u, "mm: k %u not a multiple of 8", k);
-    MOE_REQUIRE(c, experts_in_B >= 1 && (uint64_t)experts_in_B * n * ((k + BK - 1) / BK) < (1ull << 31), "mm: expert count");
+    MOE_REQUIRE(c, experts_in_B >= 1 && (uint64_t)experts_in_B * n < (1ull << 31), "mm: expert count");
+    MOE_REQUIRE(c, src_row == NULL || (mode == MOE_MM_SWIGLU_F16 && ((uintptr_t)A & 15) == 0), "mm: row gather is for the gate_up product");
     MOE_REQUIRE(c, (sa == MDA_PC_NO_SLOT && sb == MDA_PC_NO_SLOT) || amax != NULL, "mm: scale slot without amax");
     MOE_REQUIRE(c, ((uintptr_t)C & 15) == 0, "mm: C not 16-byte aligned");
     const CUtensorMap *tmA = moe_tmap_2d_f16(c, A, a_rows, k, 128, BK);
-    const uint32_t kblocks_h = (k + BK - 1) / BK;
-    // one 256-row box per stage when every column tile is a full 256 rows of one expert's matrix
-    const bool bigbox = !tiled && mode != MOE_MM_SWIGLU_F16 && n % 256u == 0 && getenv("MOE_DBG") != NULL && (atoi(getenv("MOE_DBG")) & 4);
-    const CUtensorMap *tmB = tiled ? moe_tmap_2d_f16(c, B, (uint64_t)experts_in_B * n * kblocks_h, BK, 128, BK)
-                                   : moe_tmap_2d_f16(c, B, (uint64_t)experts_in_B * n, k, bigbox ? 256 : 128, BK);
+    const CUtensorMap *tmB = moe_tmap_2d_f16(c, B, (uint64_t)experts_in_B * n, k, 128, BK);
     if (tmA == NULL || tmB == NULL) return;
     MmArgs a;
     a.C = C;
@@ -338,16 +377,17 @@ void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void
     a.sb = sb;
     a.experts_in_B = experts_in_B;
     a.prefix = prefix ? 1u : 0u;
-    a.tiled = tiled ? 1u : 0u;
-    a.bigbox = bigbox ? 1u : 0u;
-    a.dbg = getenv("MOE_DBG") ? (uint32_t)atoi(getenv("MOE_DBG")) : 0u;
+    a.src_row = src_row;
+    a.X = (const __half *)A;
+    a.ldx = k;
     a.status = c->dev_status_dev;
     uint32_t nt = mode == MOE_MM_SWIGLU_F16 ? n / BN : (n + BN - 1) / BN;
     uint64_t total = (uint64_t)(m / BM) * nt;
     uint32_t grid = total < (uint64_t)c->sm_count ? (uint32_t)total : (uint32_t)c->sm_count;
-    if (mode == MOE_MM_F32) mm_launch<MOE_MM_F32>(c, tmA, tmB, a, grid);
-    else if (mode == MOE_MM_SWIGLU_F16) mm_launch<MOE_MM_SWIGLU_F16>(c, tmA, tmB, a, grid);
-    else mm_launch<MOE_MM_F16>(c, tmA, tmB, a, grid);
+    if (mode == MOE_MM_F32) mm_launch<MOE_MM_F32, false>(c, tmA, tmB, a, grid);
+    else if (mode == MOE_MM_SWIGLU_F16 && src_row != NULL) mm_launch<MOE_MM_SWIGLU_F16, true>(c, tmA, tmB, a, grid);
+    else if (mode == MOE_MM_SWIGLU_F16) mm_launch<MOE_MM_SWIGLU_F16, false>(c, tmA, tmB, a, grid);
+    else mm_launch<MOE_MM_F16, false>(c, tmA, tmB, a, grid);
 }
 
 extern "C" void moe_cuda_mm(moe_cuda_ctx_t *c, const void *A, const void *B, float *C, const uint32_t *amax,

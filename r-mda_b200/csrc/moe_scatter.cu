@@ -95,7 +95,7 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
                          const uint32_t *__restrict__ base, const uint4 *__restrict__ x16,
                          uint4 *__restrict__ xp, uint32_t *__restrict__ slot, uint32_t pairs, uint32_t topk,
                          uint32_t d8, uint32_t ebound, uint4 *const *__restrict__ xp_peers, uint32_t experts_per_rank,
-                         uint32_t ppb) {
+                         uint32_t ppb, uint32_t *__restrict__ src_row) {
     // ppb = pairs per block (<= SC_MAX_PAIRS): 64 in the stand-alone scatter, 8*topk behind the fused router
     __shared__ uint32_t s_e[SC_MAX_PAIRS];
     __shared__ uint32_t s_slot[SC_MAX_PAIRS];
@@ -114,10 +114,13 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
             // expert-parallel: the row goes straight into the owning GPU's buffer over NVLink
             s_dst[threadIdx.x] = xp_peers != NULL ? xp_peers[e / experts_per_rank] : xp;
             slot[p0 + threadIdx.x] = p;  // :27
+            // gather mode: record where the row comes from instead of copying it; the product fetches it
+            if (src_row != NULL) src_row[p] = (p0 + threadIdx.x) / topk;
         } else {
             s_slot[threadIdx.x] = ~0u;
         }
     }
+    if (src_row != NULL) return;
     __syncthreads();
     uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     for (uint32_t q = warp; q < np; q += SC_THREADS / 32u) {
@@ -159,7 +162,7 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp,
                                                                     slot, pairs, topk, d8, ebound,
-                                                                    (uint4 *const *)xp_peers, experts_per_rank, SC_PAIRS);
+                                                                    (uint4 *const *)xp_peers, experts_per_rank, SC_PAIRS, NULL);
     MOE_LAUNCHED(c);
 }
 
@@ -176,14 +179,14 @@ void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count,
 // Ranking + row copies for blocks of 8 rows (8*topk pairs), bases from `hist`.
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
-                      void *const *xp_peers, uint32_t experts_per_rank) {
+                      void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row) {
     if (!MOE_LIVE(c)) return;
     if (rows == 0) return;
     MOE_REQUIRE(c, ((uintptr_t)x16 & 15) == 0 && ((uintptr_t)xp & 15) == 0, "scatter: rows not 16-byte aligned");
     uint32_t nblocks = (rows + 7u) / 8u;
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp, slot,
                                                                     rows * topk, topk, d8, experts,
-                                                                    (uint4 *const *)xp_peers, experts_per_rank, 8u * topk);
+                                                                    (uint4 *const *)xp_peers, experts_per_rank, 8u * topk, src_row);
     MOE_LAUNCHED(c);
 }
 
@@ -246,6 +249,6 @@ extern "C" void moe_cuda_scatter_noalloc(moe_cuda_ctx_t *c, const uint32_t *idx,
     moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts, NULL);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<(uint32_t)nblocks, SC_THREADS, 0, c->stream>>>(
-        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0, SC_PAIRS);
+        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0, SC_PAIRS, NULL);
     MOE_LAUNCHED(c);
 }

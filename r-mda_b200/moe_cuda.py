@@ -13,7 +13,7 @@ from . import build as _build
 NO_SLOT = 0xFFFFFFFF
 TILE = 128
 MOE_OK, MOE_ERR_CUDA, MOE_ERR_ARG, MOE_ERR_NOMEM, MOE_ERR_ROUTE, MOE_ERR_TIMEOUT, MOE_ERR_COMM, MOE_ERR_UNSUPPORTED = range(8)
-LAYER_UNFUSED, LAYER_YE_F32, LAYER_CHUNKED, LAYER_NO_PAIR, LAYER_WEIGHTS_TILED = 1, 2, 4, 8, 16
+LAYER_UNFUSED, LAYER_YE_F32, LAYER_CHUNKED, LAYER_NO_PAIR, LAYER_MATERIALIZE_XP = 1, 2, 4, 8, 16
 PROF_STAGES = ("route", "scan", "scatter", "gate_up", "down", "shared", "combine")
 
 
@@ -111,9 +111,6 @@ def lib() -> C.CDLL:
         L.moe_cuda_moe_rows.restype = u32
         L.moe_cuda_moe_rows.argtypes = [u32, u32, u32]
         L.moe_cuda_layer.argtypes = [vp, C.POINTER(Layer)]
-        L.moe_cuda_tiled_bytes.restype = sz
-        L.moe_cuda_tiled_bytes.argtypes = [u32, u32, u32]
-        L.moe_cuda_tile_weights.argtypes = [vp, vp, vp, u32, u32, u32]
         L.moe_cuda_ep_unique_id.restype = C.c_int
         L.moe_cuda_ep_unique_id.argtypes = [vp]
         L.moe_cuda_ep_rows.restype = u32
@@ -280,13 +277,6 @@ class Ctx:
         for k, v in kw.items():
             setattr(L, k, _ptr(v) if isinstance(v, DevBuf) or v is None else v)
         lib().moe_cuda_ep_layer(self.p, C.byref(L))
-
-    def tile_weights(self, src: DevBuf, experts: int, n: int, k: int) -> DevBuf:
-        """moe_cuda_tile_weights into a new buffer (the upload-time re-tiling)."""
-        dst = self.alloc(lib().moe_cuda_tiled_bytes(experts, n, k))
-        lib().moe_cuda_tile_weights(self.p, src.ptr, dst.ptr, experts, n, k)
-        self.flush()
-        return dst
 
     def prof(self, on: bool):
         lib().moe_cuda_prof(self.p, 1 if on else 0)
