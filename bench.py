@@ -29,9 +29,10 @@ import __graft_entry__ as entry  # noqa: E402
 METRIC = "MoE layer tokens/s (route->scatter->grouped GEMM->combine)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
-# DRAM bytes per launch of the dominant kernel (gate_up grouped product, 30B-A3B shape) from the
-# Nsight Compute capture summarised in profiles/; None until a capture of that launch exists.
-NCU_TRAFFIC_BYTES = {"c1": None}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, the
+# gate_up grouped product with row gather, at the 30B-A3B shape, from the Nsight Compute capture
+# summarised in profiles/moe_mm_kernel_30B-A3B.md (full-size launch, no scaling involved).
+NCU_TRAFFIC_BYTES = {"c1": 913420800 + 59392000}
 
 
 def peaks():
@@ -279,8 +280,10 @@ def run_ours(args):
     stages = {
         "route": {"ms": stage_ms["route"], "GB/s": gbs(route_bytes, stage_ms["route"])},
         "scan": {"ms": stage_ms["scan"]},
-        "scatter": {"ms": stage_ms["scatter"], "GB/s": gbs(scatter_bytes, stage_ms["scatter"]),
-                    "frac_hbm": gbs(scatter_bytes, stage_ms["scatter"]) / pk["hbm_gbs"]},
+        "scatter": ({"ms": stage_ms["scatter"], "GB/s": gbs(scatter_bytes, stage_ms["scatter"]),
+                     "frac_hbm": gbs(scatter_bytes, stage_ms["scatter"]) / pk["hbm_gbs"]}
+                    if args.flags & mc.LAYER_MATERIALIZE_XP else
+                    {"ms": stage_ms["scatter"], "note": "ranks and slot tables only; the gate_up product gathers the rows"}),
         "gate_up": {"ms": stage_ms["gate_up"], "TFLOP/s": tf1, "frac_tensor": tf1 / pk["bf16_tflops"],
                     "weight_GB/s": gbs(E * 2 * I * d * 2, stage_ms["gate_up"])},
         "down": {"ms": stage_ms["down"], "TFLOP/s": tf2, "frac_tensor": tf2 / pk["bf16_tflops"],
@@ -299,9 +302,9 @@ def run_ours(args):
                 "how": "three contexts take steps in turn so copies overlap kernels; wall clock between device synchronisations"},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "moe_mm_kernel<SWIGLU_F16> (gate_up grouped product)",
+        "roofline": {"bound": "tensor", "kernel": "moe_mm_kernel<SWIGLU_F16, GATHER> (gate_up grouped product, row gather + SwiGLU fused)",
                      "achieved": tf1, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": tf1 / pk["bf16_tflops"],
-                     "traffic": NCU_TRAFFIC_BYTES.get(args.config), "peak_source": pk["source"] + " (burst)",
+                     "traffic": NCU_TRAFFIC_BYTES.get(args.config) if args.flags == 0 else None, "peak_source": pk["source"] + " (burst)",
                      "flops_per_launch": gemm1_flops, "ms_per_launch": stage_ms["gate_up"]},
         "stages": stages,
     }

@@ -12,10 +12,11 @@
 //             the owning GPU's buffer (peer loads over NVLink).
 // Peer buffers are plain cudaMalloc memory mapped with CUDA IPC; all accesses
 // are ordinary ld/st (no multimem, no TMA from peer memory: the grouped
-// products only ever read local HBM).  NCCL carries what is left: the
-// per-expert counts (one all-gather) and two stream-ordered barriers (4-byte
-// all-reduces) that separate "all rows landed" from the products and "all
-// products done" from the combine.
+// products only ever read local HBM).  The per-expert counts travel the same way
+// (each rank stores its row into every peer's table) and the three points where
+// all ranks must have caught up -- counts complete, all rows landed, all products
+// done -- are flag barriers over peer memory with bounded waits.  NCCL is used
+// once, at set-up, to exchange the IPC handles.
 //
 // Row order inside an expert is (source rank, token index); with contiguous
 // token blocks per rank that is the global token order, so the permutation is
@@ -66,6 +67,8 @@ static bool moe_nccl_load(char *why, size_t n) {
 }
 
 #define MOE_EP_MAX_WORLD 16
+#define EP_FLAG_WORDS 64u  // 3 barrier sites x 16 ranks of epoch flags, padded
+#define EP_WAIT_NS 2000000000ull
 
 struct moe_ep_state {
     ncclComm_t comm;
@@ -77,7 +80,11 @@ struct moe_ep_state {
     void *xp_peer[MOE_EP_MAX_WORLD];     // every rank's xp as mapped here (own entry = local pointer)
     void *ye_peer[MOE_EP_MAX_WORLD];
     void **xp_peer_dev, **ye_peer_dev;   // the same tables in device memory
-    uint32_t *cnt_all;                   // [world][experts]
+    uint32_t *cnt_all;                   // [world][experts], inside sync (written by the peers)
+    uint32_t *sync;                      // peer-visible: 3 x 16 epoch flags, then cnt_all
+    void *sync_peer[MOE_EP_MAX_WORLD];
+    void **sync_peer_dev;
+    uint32_t epoch;
     uint32_t *dst_off;                   // [experts]: first row of this rank's rows in the owner's buffer
     uint32_t *tiles;                     // [mcap/128] local tile schedule
     uint32_t *idx, *slot, *count, *bar;
@@ -119,8 +126,9 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
         if (r == ep->rank) continue;
         if (ep->xp_peer[r] != NULL) cudaIpcCloseMemHandle(ep->xp_peer[r]);
         if (ep->ye_peer[r] != NULL) cudaIpcCloseMemHandle(ep->ye_peer[r]);
+        if (ep->sync_peer[r] != NULL) cudaIpcCloseMemHandle(ep->sync_peer[r]);
     }
-    void *mine[] = {ep->xp, ep->ye, ep->hp16, ep->xp_peer_dev, ep->ye_peer_dev, ep->cnt_all, ep->dst_off,
+    void *mine[] = {ep->xp, ep->ye, ep->hp16, ep->xp_peer_dev, ep->ye_peer_dev, ep->sync_peer_dev, ep->sync, ep->dst_off,
                     ep->tiles, ep->idx, ep->slot, ep->count, ep->bar, ep->wt};
     for (size_t i = 0; i < sizeof(mine) / sizeof(mine[0]); i += 1) {
         if (mine[i] != NULL) cudaFree(mine[i]);
@@ -173,7 +181,9 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     ep->hp16 = (__half *)moe_cuda_alloc(c, (size_t)mcap * cfg->inter * 2);
     ep->xp_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
     ep->ye_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
-    ep->cnt_all = (uint32_t *)moe_cuda_alloc(c, (size_t)world * E * 4);
+    ep->sync = (uint32_t *)moe_cuda_alloc(c, (EP_FLAG_WORDS + (size_t)world * E) * 4);
+    ep->cnt_all = ep->sync == NULL ? NULL : ep->sync + EP_FLAG_WORDS;
+    ep->sync_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
     ep->dst_off = (uint32_t *)moe_cuda_alloc(c, E * 4);
     ep->tiles = (uint32_t *)moe_cuda_alloc(c, (size_t)(mcap / MOE_TILE) * 4);
     ep->idx = (uint32_t *)moe_cuda_alloc(c, R * K * 4);
@@ -183,14 +193,16 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     ep->bar = (uint32_t *)moe_cuda_alloc(c, 256);
     if (c->status != MOE_OK) return;
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->bar, 0, 256, c->stream));
+    MOE_CUDA_TRY(c, cudaMemsetAsync(ep->sync, 0, (EP_FLAG_WORDS + (size_t)world * E) * 4, c->stream));
 
     // Exchange the IPC handles of xp and ye through the communicator itself.
     struct Handles {
-        cudaIpcMemHandle_t xp, ye;
+        cudaIpcMemHandle_t xp, ye, sync;
     };
     Handles mine;
     MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.xp, ep->xp));
     MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.ye, ep->ye));
+    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.sync, ep->sync));
     Handles *d_all = (Handles *)moe_cuda_alloc(c, sizeof(Handles) * (size_t)world);
     if (d_all == NULL) return;
     MOE_CUDA_TRY(c, cudaMemcpyAsync(d_all + rank, &mine, sizeof(mine), cudaMemcpyHostToDevice, c->stream));
@@ -203,26 +215,79 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
         if (r == rank) {
             ep->xp_peer[r] = ep->xp;
             ep->ye_peer[r] = ep->ye;
+            ep->sync_peer[r] = ep->sync;
             continue;
         }
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->xp_peer[r], all[r].xp, cudaIpcMemLazyEnablePeerAccess));
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->ye_peer[r], all[r].ye, cudaIpcMemLazyEnablePeerAccess));
+        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->sync_peer[r], all[r].sync, cudaIpcMemLazyEnablePeerAccess));
     }
     MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->xp_peer_dev, ep->xp_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
     MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->ye_peer_dev, ep->ye_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
+    MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->sync_peer_dev, ep->sync_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
     // nobody may write into a peer before every rank has finished mapping
     MOE_NCCL_TRY(c, g_nccl.AllReduce(ep->bar, ep->bar + 8, 1, ncclUint32, ncclSum, ep->comm, c->stream));
     MOE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
 }
 
+// Cross-GPU barrier without a library call: every rank stores the epoch into its
+// slot of every peer's flag row, then waits until all slots of its own row have
+// reached the epoch.  Flags only ever grow.  The wait is bounded (2 s): on
+// timeout the kernel records MOE_ERR_TIMEOUT and returns, it never hangs.
+__device__ __forceinline__ void ep_signal_and_wait(uint32_t *const *sync_peers, uint32_t world, uint32_t rank, uint32_t site,
+                                                   uint32_t epoch, uint32_t *status) {
+    // called by threads 0..world-1 of a block after a __syncthreads(); thread p talks to rank p
+    uint32_t p = threadIdx.x;
+    if (p < world) {
+        __threadfence_system();
+        uint32_t *theirs = sync_peers[p] + site * MOE_EP_MAX_WORLD + rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+        const uint32_t *mine = sync_peers[rank] + site * MOE_EP_MAX_WORLD + p;
+        uint64_t t0 = 0;
+        for (uint32_t spins = 0;; spins += 1) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if ((int32_t)(v - epoch) >= 0) break;
+            if ((spins & 0x3ffu) == 0x3ffu) {
+                uint64_t now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) {
+                    t0 = now;
+                } else if (now - t0 > EP_WAIT_NS) {
+                    atomicCAS(status, 0u, (uint32_t)MOE_ERR_TIMEOUT | ((20u + site) << 8));
+                    break;
+                }
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(32)
+moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t world, uint32_t rank, uint32_t site, uint32_t epoch,
+                      uint32_t *status) {
+    ep_signal_and_wait(sync_peers, world, rank, site, epoch, status);
+}
+
 // From all ranks' per-expert counts: where this rank's rows of expert e start in
 // the owner's buffer (dst_off), and the owner-side tile schedule of this rank's
 // own experts.  One block of 512 threads, thread = global expert.
+// The counts exchange is part of this kernel: each rank stores its counts row
+// into every peer's table, a flag barrier makes all rows visible, then the plan
+// is computed -- one launch instead of an all-gather plus a kernel.
 __global__ void __launch_bounds__(512)
-moe_ep_plan_kernel(const uint32_t *__restrict__ cnt_all, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
+moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch,
+                   uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
                    uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status) {
     __shared__ uint32_t incl_s[512];
     uint32_t e = threadIdx.x;
+    if (e < experts) {
+        uint32_t v = my_count[e];
+        for (uint32_t p = 0; p < world; p += 1) sync_peers[p][EP_FLAG_WORDS + rank * experts + e] = v;
+    }
+    __syncthreads();
+    ep_signal_and_wait(sync_peers, world, rank, 0, epoch, status);
+    __syncthreads();
+    const volatile uint32_t *cnt_all = sync_peers[rank] + EP_FLAG_WORDS;
     uint32_t tot = 0, before = 0;
     if (e < experts) {
         for (uint32_t s = 0; s < world; s += 1) {
@@ -290,16 +355,18 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
     mark(1);
     if (!MOE_LIVE(c)) return;
     // counts of every rank (also orders this layer after every peer's previous combine)
-    MOE_NCCL_TRY(c, g_nccl.AllGather(count, ep->cnt_all, E, ncclUint32, ep->comm, c->stream));
-    moe_ep_plan_kernel<<<1, 512, 0, c->stream>>>(ep->cnt_all, ep->dst_off, ep->tiles, E, (uint32_t)ep->world,
-                                                 (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev);
+    ep->epoch += 1;
+    moe_ep_plan_kernel<<<1, 512, 0, c->stream>>>(count, (uint32_t *const *)ep->sync_peer_dev, ep->epoch, ep->dst_off, ep->tiles,
+                                                 E, (uint32_t)ep->world, (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev);
     MOE_LAUNCHED(c);
     if (L->off != NULL) moe_cuda_copy(c, L->off, ep->dst_off, (size_t)E * 4);
     mark(2);
     // dispatch fused into the scatter: rows go to their owner's xp
     if (R != 0) moe_launch_place(c, idx, ep->dst_off, hist, L->x16, ep->xp, slot, R, K, d / 8u, E, ep->xp_peer_dev, ep->el);
     if (!MOE_LIVE(c)) return;
-    MOE_NCCL_TRY(c, g_nccl.AllReduce(ep->bar, ep->bar + 8, 1, ncclUint32, ncclSum, ep->comm, c->stream));  // all rows landed
+    moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world, (uint32_t)ep->rank, 1,
+                                                   ep->epoch, c->dev_status_dev);  // all rows landed
+    MOE_LAUNCHED(c);
     mark(3);
     moe_launch_mm(c, MOE_MM_SWIGLU_F16, ep->xp, L->wgu, ep->hp16, NULL, ep->tiles, mcap, 2u * I, d, MDA_PC_NO_SLOT,
                   MDA_PC_NO_SLOT, ep->el, mcap, true);
@@ -308,7 +375,9 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
                   MDA_PC_NO_SLOT, ep->el, mcap, true);
     mark(5);
     if (!MOE_LIVE(c)) return;
-    MOE_NCCL_TRY(c, g_nccl.AllReduce(ep->bar, ep->bar + 8, 1, ncclUint32, ncclSum, ep->comm, c->stream));  // all products done
+    moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world, (uint32_t)ep->rank, 2,
+                                                   ep->epoch, c->dev_status_dev);  // all products done
+    MOE_LAUNCHED(c);
     mark(6);
     if (R != 0) {
         moe_combine_args a = {};

@@ -14,8 +14,6 @@
 // rows + the matching 64 up rows, so lanes i and i+64 pair up: the "up" warps
 // hand their values to the "gate" warps through shared memory, which apply
 // silu(gate)*up (shader/qwen_elem.comp:20-31 op 0) and store fp16.
-#include <stdlib.h>
-
 #include "moe_tc.cuh"
 
 namespace {
@@ -58,7 +56,6 @@ struct SwArgs {
     uint32_t n;                // weight rows per expert (2*inter, or d)
     uint32_t k;
     uint32_t ldc;              // row stride of C in elements
-    uint32_t dbg;              // experiment switches
     uint32_t *status;
 };
 
@@ -250,7 +247,6 @@ moe_mm_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                     const uint64_t ad = umma_desc(base), bd = umma_desc(base + A_BYTES);
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
-                        if (a.dbg & 8u) continue;
                         if (PAIR == 2) umma_f16_pair(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
                         else umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
@@ -295,7 +291,7 @@ moe_mm_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             }
             tc_fence_after();
             const uint32_t taddr = tmem_base + as * MAX_TOK + ((q * 32u) << 16);
-            const uint32_t nch = (a.dbg & 2u) ? 0u : (it.ntok + 31u) / 32u;
+            const uint32_t nch = (it.ntok + 31u) / 32u;
             if (MODE == MOE_MM_SWIGLU_F16) {
                 // lanes 0..63 hold gate features, lanes 64..127 the matching up features
                 const uint32_t f = (it.ft * PAIR + rank) * 64u + (q & 1u) * 32u + lane;
@@ -316,7 +312,7 @@ moe_mm_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                         for (uint32_t j = 0; j < 32; j += 1) {
                             float g = __uint_as_float(v[j]);
                             float h = __fdividef(g, 1.0f + __expf(-g)) * exb[j];
-                            if (t0 + j < it.nvalid && !(a.dbg & 1u)) out[(size_t)(t0 + j) * a.ldc] = __float2half_rn(h);
+                            if (t0 + j < it.nvalid) out[(size_t)(t0 + j) * a.ldc] = __float2half_rn(h);
                         }
                     }
                     exbuf ^= 1u;
@@ -332,7 +328,7 @@ moe_mm_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                         __half *out = reinterpret_cast<__half *>(a.C) + (size_t)(it.row0 + t0) * a.ldc + cfeat;
 #pragma unroll
                         for (uint32_t j = 0; j < 32; j += 1) {
-                            if (t0 + j < it.nvalid && !(a.dbg & 1u)) out[(size_t)j * a.ldc] = __float2half_rn(__uint_as_float(v[j]));
+                            if (t0 + j < it.nvalid) out[(size_t)j * a.ldc] = __float2half_rn(__uint_as_float(v[j]));
                         }
                     } else {
                         float *out = reinterpret_cast<float *>(a.C) + (size_t)(it.row0 + t0) * a.ldc + cfeat;
@@ -446,7 +442,6 @@ void moe_launch_mm_swap(moe_cuda_ctx *c, int mode, int pair, const void *X, uint
     a.k = k;
     a.ldc = ldc;
     a.status = c->dev_status_dev;
-    a.dbg = getenv("MOE_DBG") ? (uint32_t)atoi(getenv("MOE_DBG")) : 0u;
     uint32_t ft = mode == MOE_MM_SWIGLU_F16 ? (n / 2u) / (64u * (uint32_t)pair) : n / (128u * (uint32_t)pair);
     uint64_t total = (uint64_t)max_chunks * ft * (uint32_t)pair;
     uint32_t sms = (uint32_t)c->sm_count / (uint32_t)pair * (uint32_t)pair;
