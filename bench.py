@@ -333,6 +333,7 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=1 << 30, help="tokens per CPU sample/step (default: the whole workload)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--flags", type=int, default=0, help="MOE_LAYER_* flags passed to moe_cuda_layer")
+    ap.add_argument("--micro-batches", type=int, default=0, help="expert parallel: token slices per layer (0 = automatic)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -29,7 +29,7 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
 
     uid = [mc.ep_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
-    ctx.ep_init(uid[0], rank, world, E, K, d, I, T)
+    ctx.ep_init(uid[0], rank, world, E, K, d, I, T, args.micro_batches)
     d_wgu, d_wdown = ctx.upload(wgu), ctx.upload(wdown)
     d_proj, d_x = ctx.upload(proj), ctx.upload(x16)
     d_h = ctx.zeros(T * d * 4)

@@ -197,6 +197,8 @@ void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
 typedef struct moe_cuda_ep_cfg_t {
     uint32_t experts, topk, d, inter; /* global expert count; experts % world == 0, inter % 128 == 0 */
     uint32_t max_rows;                /* most tokens any rank will pass in one call */
+    uint32_t micro_batches;           /* 1 or 2 slices of the local tokens that pipeline NVLink transfers against
+                                         the products; 0 = automatic (2 from 4 ranks on) */
 } moe_cuda_ep_cfg_t;
 /* 128 bytes of NCCL unique id: call on one rank, hand the bytes to all. */
 int moe_cuda_ep_unique_id(void *out128);
@@ -208,8 +210,9 @@ void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, int rank, int
                       const moe_cuda_ep_cfg_t *cfg);
 /* Collective: one MoE layer.  L->rows = this rank's tokens, L->experts = global
  * expert count, L->wgu / L->wdown = this rank's experts only.  L->slot receives
- * row numbers inside the owning rank's buffer, L->off this rank's first row per
- * expert there.  Shared expert, L->tiles and the flags are not supported. */
+ * row numbers inside the owning rank's buffer (of the token's micro-batch),
+ * L->off (one micro-batch only) this rank's first row per expert there.  Shared
+ * expert, L->tiles and the flags are not supported. */
 void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
 
 /* Per-stage device times of the last moe_cuda_layer call, in milliseconds, in

@@ -67,28 +67,33 @@ static bool moe_nccl_load(char *why, size_t n) {
 }
 
 #define MOE_EP_MAX_WORLD 16
-#define EP_FLAG_WORDS 64u  // 3 barrier sites x 16 ranks of epoch flags, padded
+#define EP_FLAG_WORDS 128u  // 6 barrier sites (3 per micro-batch) x 16 ranks of epoch flags, padded
 #define EP_WAIT_NS 2000000000ull
+
+#define EP_MAX_MB 2  // micro-batches per layer call
 
 struct moe_ep_state {
     ncclComm_t comm;
     int rank, world;
     moe_cuda_ep_cfg_t cfg;
     uint32_t el;          // experts per rank
-    uint32_t mcap;        // rows of the local expert-contiguous buffers
-    __half *xp, *ye, *hp16;              // local [mcap x d], [mcap x d], [mcap x inter]
+    uint32_t nmb;         // micro-batches: the local tokens are cut in nmb parts that pipeline transfer against products
+    uint32_t mcap;        // rows of the expert-contiguous buffers of ONE micro-batch
+    __half *xp, *ye, *hp16;              // local [nmb * mcap x d], [nmb * mcap x d], [nmb * mcap x inter]
     void *xp_peer[MOE_EP_MAX_WORLD];     // every rank's xp as mapped here (own entry = local pointer)
     void *ye_peer[MOE_EP_MAX_WORLD];
-    void **xp_peer_dev, **ye_peer_dev;   // the same tables in device memory
-    uint32_t *cnt_all;                   // [world][experts], inside sync (written by the peers)
-    uint32_t *sync;                      // peer-visible: 3 x 16 epoch flags, then cnt_all
+    void **xp_peer_dev[EP_MAX_MB], **ye_peer_dev[EP_MAX_MB];  // per micro-batch: each rank's buffer of that micro-batch
+    uint32_t *sync;                      // peer-visible: 6 x 16 epoch flags, then nmb tables [world][experts] of counts
     void *sync_peer[MOE_EP_MAX_WORLD];
     void **sync_peer_dev;
     uint32_t epoch;
-    uint32_t *dst_off;                   // [experts]: first row of this rank's rows in the owner's buffer
-    uint32_t *tiles;                     // [mcap/128] local tile schedule
-    uint32_t *idx, *slot, *count, *bar;
+    uint32_t *dst_off[EP_MAX_MB];        // [experts]: first row of this rank's rows in the owner's buffer
+    uint32_t *tiles[EP_MAX_MB];          // [mcap/128] local tile schedule
+    uint32_t *count[EP_MAX_MB];
+    uint32_t *idx, *slot, *bar;
     float *wt;
+    cudaStream_t side;                   // second stream: micro-batch 1
+    cudaEvent_t ev_fork, ev_disp, ev_join;
 };
 
 #define MOE_NCCL_TRY(c, expr)                                                                   \
@@ -128,8 +133,16 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
         if (ep->ye_peer[r] != NULL) cudaIpcCloseMemHandle(ep->ye_peer[r]);
         if (ep->sync_peer[r] != NULL) cudaIpcCloseMemHandle(ep->sync_peer[r]);
     }
-    void *mine[] = {ep->xp, ep->ye, ep->hp16, ep->xp_peer_dev, ep->ye_peer_dev, ep->sync_peer_dev, ep->sync, ep->dst_off,
-                    ep->tiles, ep->idx, ep->slot, ep->count, ep->bar, ep->wt};
+    void *mine[] = {ep->xp, ep->ye, ep->hp16, ep->xp_peer_dev[0], ep->ye_peer_dev[0], ep->xp_peer_dev[1], ep->ye_peer_dev[1],
+                    ep->sync_peer_dev, ep->sync, ep->dst_off[0], ep->dst_off[1], ep->tiles[0], ep->tiles[1], ep->count[0],
+                    ep->count[1], ep->idx, ep->slot, ep->bar, ep->wt};
+    if (ep->side != NULL) {
+        cudaStreamSynchronize(ep->side);
+        cudaStreamDestroy(ep->side);
+        cudaEventDestroy(ep->ev_fork);
+        cudaEventDestroy(ep->ev_disp);
+        cudaEventDestroy(ep->ev_join);
+    }
     for (size_t i = 0; i < sizeof(mine) / sizeof(mine[0]); i += 1) {
         if (mine[i] != NULL) cudaFree(mine[i]);
     }
@@ -158,7 +171,12 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
         moe_fail(c, MOE_ERR_COMM, "%s", why);
         return;
     }
-    uint32_t mcap = moe_cuda_ep_rows((uint32_t)world, cfg->max_rows, cfg->experts, cfg->topk);
+    MOE_REQUIRE(c, cfg->micro_batches <= EP_MAX_MB, "ep_init: micro_batches %u > %d", cfg->micro_batches, EP_MAX_MB);
+    // 0 = automatic: with 4 or more ranks most rows cross NVLink, and cutting the tokens in two lets one
+    // half's transfers run under the other half's products
+    uint32_t nmb = cfg->micro_batches != 0 ? cfg->micro_batches : (world >= 4 ? 2u : 1u);
+    uint32_t rows_mb = nmb == 1 ? cfg->max_rows : (((cfg->max_rows + 1u) / 2u + 7u) & ~7u);
+    uint32_t mcap = moe_cuda_ep_rows((uint32_t)world, rows_mb, cfg->experts, cfg->topk);
     MOE_REQUIRE(c, mcap != 0, "ep_init: buffer rows overflow");
     moe_ep_state *ep = (moe_ep_state *)calloc(1, sizeof(moe_ep_state));
     if (ep == NULL) {
@@ -171,29 +189,38 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     ep->cfg = *cfg;
     ep->el = cfg->experts / (uint32_t)world;
     ep->mcap = mcap;
+    ep->nmb = nmb;
     ncclUniqueId id;
     memcpy(&id, unique_id128, sizeof(id));
     MOE_NCCL_TRY(c, g_nccl.CommInitRank(&ep->comm, world, id, rank));
 
     size_t R = cfg->max_rows, K = cfg->topk, E = cfg->experts;
-    ep->xp = (__half *)moe_cuda_alloc(c, (size_t)mcap * cfg->d * 2);
-    ep->ye = (__half *)moe_cuda_alloc(c, (size_t)mcap * cfg->d * 2);
-    ep->hp16 = (__half *)moe_cuda_alloc(c, (size_t)mcap * cfg->inter * 2);
-    ep->xp_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
-    ep->ye_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
-    ep->sync = (uint32_t *)moe_cuda_alloc(c, (EP_FLAG_WORDS + (size_t)world * E) * 4);
-    ep->cnt_all = ep->sync == NULL ? NULL : ep->sync + EP_FLAG_WORDS;
+    const size_t sync_words = EP_FLAG_WORDS + (size_t)nmb * world * E;
+    ep->xp = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->d * 2);
+    ep->ye = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->d * 2);
+    ep->hp16 = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->inter * 2);
+    ep->sync = (uint32_t *)moe_cuda_alloc(c, sync_words * 4);
     ep->sync_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
-    ep->dst_off = (uint32_t *)moe_cuda_alloc(c, E * 4);
-    ep->tiles = (uint32_t *)moe_cuda_alloc(c, (size_t)(mcap / MOE_TILE) * 4);
+    for (uint32_t m = 0; m < nmb; m += 1) {
+        ep->xp_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+        ep->ye_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+        ep->dst_off[m] = (uint32_t *)moe_cuda_alloc(c, E * 4);
+        ep->tiles[m] = (uint32_t *)moe_cuda_alloc(c, (size_t)(mcap / MOE_TILE) * 4);
+        ep->count[m] = (uint32_t *)moe_cuda_alloc(c, E * 4);
+    }
     ep->idx = (uint32_t *)moe_cuda_alloc(c, R * K * 4);
     ep->slot = (uint32_t *)moe_cuda_alloc(c, R * K * 4);
     ep->wt = (float *)moe_cuda_alloc(c, R * K * 4);
-    ep->count = (uint32_t *)moe_cuda_alloc(c, E * 4);
     ep->bar = (uint32_t *)moe_cuda_alloc(c, 256);
     if (c->status != MOE_OK) return;
+    if (nmb > 1) {
+        MOE_CUDA_TRY(c, cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking));
+        MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_fork, cudaEventDisableTiming));
+        MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_disp, cudaEventDisableTiming));
+        MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_join, cudaEventDisableTiming));
+    }
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->bar, 0, 256, c->stream));
-    MOE_CUDA_TRY(c, cudaMemsetAsync(ep->sync, 0, (EP_FLAG_WORDS + (size_t)world * E) * 4, c->stream));
+    MOE_CUDA_TRY(c, cudaMemsetAsync(ep->sync, 0, sync_words * 4, c->stream));
 
     // Exchange the IPC handles of xp and ye through the communicator itself.
     struct Handles {
@@ -222,8 +249,15 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->ye_peer[r], all[r].ye, cudaIpcMemLazyEnablePeerAccess));
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->sync_peer[r], all[r].sync, cudaIpcMemLazyEnablePeerAccess));
     }
-    MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->xp_peer_dev, ep->xp_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
-    MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->ye_peer_dev, ep->ye_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
+    for (uint32_t m = 0; m < nmb; m += 1) {  // micro-batch m lives at row m * mcap of every rank's buffers
+        void *xt[MOE_EP_MAX_WORLD] = {}, *yt[MOE_EP_MAX_WORLD] = {};
+        for (int r = 0; r < world; r += 1) {
+            xt[r] = (__half *)ep->xp_peer[r] + (size_t)m * mcap * cfg->d;
+            yt[r] = (__half *)ep->ye_peer[r] + (size_t)m * mcap * cfg->d;
+        }
+        MOE_CUDA_TRY(c, cudaMemcpy(ep->xp_peer_dev[m], xt, sizeof(xt), cudaMemcpyHostToDevice));
+        MOE_CUDA_TRY(c, cudaMemcpy(ep->ye_peer_dev[m], yt, sizeof(yt), cudaMemcpyHostToDevice));
+    }
     MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->sync_peer_dev, ep->sync_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
     // nobody may write into a peer before every rank has finished mapping
     MOE_NCCL_TRY(c, g_nccl.AllReduce(ep->bar, ep->bar + 8, 1, ncclUint32, ncclSum, ep->comm, c->stream));
@@ -275,19 +309,19 @@ moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t world, uint32_t rank
 // into every peer's table, a flag barrier makes all rows visible, then the plan
 // is computed -- one launch instead of an all-gather plus a kernel.
 __global__ void __launch_bounds__(512)
-moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch,
-                   uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
+moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch, uint32_t site,
+                   uint32_t table_off, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
                    uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status) {
     __shared__ uint32_t incl_s[512];
     uint32_t e = threadIdx.x;
     if (e < experts) {
         uint32_t v = my_count[e];
-        for (uint32_t p = 0; p < world; p += 1) sync_peers[p][EP_FLAG_WORDS + rank * experts + e] = v;
+        for (uint32_t p = 0; p < world; p += 1) sync_peers[p][table_off + rank * experts + e] = v;
     }
     __syncthreads();
-    ep_signal_and_wait(sync_peers, world, rank, 0, epoch, status);
+    ep_signal_and_wait(sync_peers, world, rank, site, epoch, status);
     __syncthreads();
-    const volatile uint32_t *cnt_all = sync_peers[rank] + EP_FLAG_WORDS;
+    const volatile uint32_t *cnt_all = sync_peers[rank] + table_off;
     uint32_t tot = 0, before = 0;
     if (e < experts) {
         for (uint32_t s = 0; s < world; s += 1) {
@@ -333,77 +367,102 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
     MOE_REQUIRE(c, L->shared == 0, "ep_layer: the shared expert is not part of the expert-parallel path");
     MOE_REQUIRE(c, L->hc >= 1, "ep_layer: hc 0");
     const uint32_t R = L->rows, K = L->topk, E = L->experts, d = L->d, I = L->inter;
-    const uint32_t mcap = ep->mcap;
+    const uint32_t mcap = ep->mcap, nmb = ep->nmb;
     uint32_t *idx = L->idx != NULL ? L->idx : ep->idx;
     uint32_t *slot = L->slot != NULL ? L->slot : ep->slot;
-    uint32_t *count = L->count != NULL ? L->count : ep->count;
     float *wt = L->wt != NULL ? L->wt : ep->wt;
+    cudaStream_t main_stream = c->stream;
 
     auto mark = [&](int i) {
-        if (c->prof && c->ev_made && c->status == MOE_OK) cudaEventRecord(c->ev[i], c->stream);
+        if (c->prof && c->ev_made && c->status == MOE_OK) cudaEventRecord(c->ev[i], main_stream);
     };
     mark(0);
-    moe_cuda_fill(c, ep->tiles, (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
+    for (uint32_t m = 0; m < nmb; m += 1) moe_cuda_fill(c, ep->tiles[m], (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
     uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)((R + 7u) / 8u + 1u) * E * 4);
     if (hist == NULL) return;
-    if (R != 0) {
-        moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride);
-        moe_launch_colscan_counts(c, hist, count, R, E);
-    } else {
-        moe_cuda_fill(c, count, (size_t)E * 4, 0);
-    }
+    if (R != 0) moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride);
     mark(1);
     if (!MOE_LIVE(c)) return;
-    // counts of every rank (also orders this layer after every peer's previous combine)
     ep->epoch += 1;
-    moe_ep_plan_kernel<<<1, 512, 0, c->stream>>>(count, (uint32_t *const *)ep->sync_peer_dev, ep->epoch, ep->dst_off, ep->tiles,
-                                                 E, (uint32_t)ep->world, (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev);
-    MOE_LAUNCHED(c);
-    if (L->off != NULL) moe_cuda_copy(c, L->off, ep->dst_off, (size_t)E * 4);
-    mark(2);
-    // dispatch fused into the scatter: rows go to their owner's xp
-    if (R != 0) moe_launch_place(c, idx, ep->dst_off, hist, L->x16, ep->xp, slot, R, K, d / 8u, E, ep->xp_peer_dev, ep->el);
-    if (!MOE_LIVE(c)) return;
-    moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world, (uint32_t)ep->rank, 1,
-                                                   ep->epoch, c->dev_status_dev);  // all rows landed
-    MOE_LAUNCHED(c);
-    mark(3);
-    moe_launch_mm(c, MOE_MM_SWIGLU_F16, ep->xp, L->wgu, ep->hp16, NULL, ep->tiles, mcap, 2u * I, d, MDA_PC_NO_SLOT,
-                  MDA_PC_NO_SLOT, ep->el, mcap, true);
-    mark(4);
-    moe_launch_mm(c, MOE_MM_F16, ep->hp16, L->wdown, ep->ye, NULL, ep->tiles, mcap, d, I, MDA_PC_NO_SLOT,
-                  MDA_PC_NO_SLOT, ep->el, mcap, true);
-    mark(5);
-    if (!MOE_LIVE(c)) return;
-    moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world, (uint32_t)ep->rank, 2,
-                                                   ep->epoch, c->dev_status_dev);  // all products done
-    MOE_LAUNCHED(c);
-    mark(6);
-    if (R != 0) {
-        moe_combine_args a = {};
-        a.wt = wt;
-        a.slot = slot;
-        a.y = ep->ye;
-        a.proj = L->proj;
-        a.inj = L->inj;
-        a.h = L->h;
-        a.x16 = (const __half *)L->x16;
-        a.y16 = (__half *)L->y16;
-        a.eps = L->eps;
-        a.rows = R;
-        a.d = d;
-        a.topk = K;
-        a.pstride = L->pstride;
-        a.sg_off = E;
-        a.inj_stride = L->inj_stride;
-        a.inj_off = L->inj_off;
-        a.hc = L->hc;
-        a.y_is_f16 = true;
-        a.idx = idx;
-        a.y_peers = (const void *const *)ep->ye_peer_dev;
-        a.experts_per_rank = ep->el;
-        moe_launch_combine(c, a);  // return all-to-all fused into the gather
+    // rows of micro-batch 0: the first half, rounded to the router's 8-row blocks
+    const uint32_t r0 = nmb == 1 ? R : (R < (((R + 1u) / 2u + 7u) & ~7u) ? R : (((R + 1u) / 2u + 7u) & ~7u));
+    if (nmb > 1) {
+        MOE_CUDA_TRY(c, cudaEventRecord(ep->ev_fork, main_stream));
+        MOE_CUDA_TRY(c, cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
     }
-    mark(7);
+    for (uint32_t m = 0; m < nmb; m += 1) {
+        // Micro-batch m runs on its own stream; every rank issues the same sequence, also for an empty slice.
+        const uint32_t row0 = m == 0 ? 0u : r0, rows = m == 0 ? r0 : R - r0;
+        const uint32_t site = 3u * m;
+        c->stream = m == 0 ? main_stream : ep->side;
+        uint32_t *count = (m == 0 && nmb == 1 && L->count != NULL) ? L->count : ep->count[m];
+        if (rows != 0) moe_launch_colscan_counts(c, hist + (size_t)(row0 / 8u) * E, count, rows, E);
+        else moe_cuda_fill(c, count, (size_t)E * 4, 0);
+        // counts of every rank + plan (also orders this layer after every peer's previous combine)
+        moe_ep_plan_kernel<<<1, 512, 0, c->stream>>>(count, (uint32_t *const *)ep->sync_peer_dev, ep->epoch, site,
+                                                     EP_FLAG_WORDS + m * (uint32_t)ep->world * E, ep->dst_off[m], ep->tiles[m], E,
+                                                     (uint32_t)ep->world, (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev);
+        c->launches += 1;
+        if (m == 0) {
+            if (L->off != NULL && nmb == 1) moe_cuda_copy(c, L->off, ep->dst_off[0], (size_t)E * 4);
+            mark(2);
+        } else {
+            // stagger: this slice's rows go out once the first slice's are on their way, under its products
+            cudaStreamWaitEvent(c->stream, ep->ev_disp, 0);
+        }
+        // dispatch fused into the scatter: rows go straight into their owner's buffer
+        if (rows != 0) {
+            moe_launch_place(c, idx + (size_t)row0 * K, ep->dst_off[m], hist + (size_t)(row0 / 8u) * E,
+                             (const __half *)L->x16 + (size_t)row0 * d, ep->xp + (size_t)m * mcap * d,
+                             slot + (size_t)row0 * K, rows, K, d / 8u, E, ep->xp_peer_dev[m], ep->el);
+        }
+        if (m == 0 && nmb > 1) cudaEventRecord(ep->ev_disp, c->stream);
+        moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
+                                                       (uint32_t)ep->rank, site + 1u, ep->epoch, c->dev_status_dev);  // all rows landed
+        c->launches += 1;
+        if (m == 0) mark(3);
+        moe_launch_mm(c, MOE_MM_SWIGLU_F16, ep->xp + (size_t)m * mcap * d, L->wgu, ep->hp16 + (size_t)m * mcap * I, NULL,
+                      ep->tiles[m], mcap, 2u * I, d, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);
+        if (m == 0) mark(4);
+        moe_launch_mm(c, MOE_MM_F16, ep->hp16 + (size_t)m * mcap * I, L->wdown, ep->ye + (size_t)m * mcap * d, NULL,
+                      ep->tiles[m], mcap, d, I, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);
+        if (m == 0) mark(5);
+        moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
+                                                       (uint32_t)ep->rank, site + 2u, ep->epoch, c->dev_status_dev);  // all products done
+        c->launches += 1;
+        if (m == 0) mark(6);
+        if (rows != 0) {
+            moe_combine_args a = {};
+            a.wt = wt + (size_t)row0 * K;
+            a.slot = slot + (size_t)row0 * K;
+            a.y = ep->ye + (size_t)m * mcap * d;
+            a.proj = L->proj + (size_t)row0 * L->pstride;
+            a.inj = L->inj != NULL ? L->inj + (size_t)row0 * L->inj_stride : NULL;
+            a.h = L->h != NULL ? L->h + (size_t)row0 * L->hc * d : NULL;
+            a.x16 = (const __half *)L->x16 + (size_t)row0 * d;
+            a.y16 = L->y16 != NULL ? (__half *)L->y16 + (size_t)row0 * d : NULL;
+            a.eps = L->eps;
+            a.rows = rows;
+            a.d = d;
+            a.topk = K;
+            a.pstride = L->pstride;
+            a.sg_off = E;
+            a.inj_stride = L->inj_stride;
+            a.inj_off = L->inj_off;
+            a.hc = L->hc;
+            a.y_is_f16 = true;
+            a.idx = idx + (size_t)row0 * K;
+            a.y_peers = (const void *const *)ep->ye_peer_dev[m];
+            a.experts_per_rank = ep->el;
+            moe_launch_combine(c, a);  // return all-to-all fused into the gather
+        }
+        if (m == 0) mark(7);
+    }
+    c->stream = main_stream;
+    if (nmb > 1) {
+        cudaEventRecord(ep->ev_join, ep->side);
+        cudaStreamWaitEvent(main_stream, ep->ev_join, 0);
+    }
+    if (cudaGetLastError() != cudaSuccess) moe_fail(c, MOE_ERR_CUDA, "ep_layer: launch failed");
     if (c->prof && c->ev_made && c->status == MOE_OK) c->ev_valid = true;
 }

@@ -22,7 +22,8 @@ def main():
     pkg = entry.load_package()
     mc, synth, epp = pkg.moe_cuda, pkg.synth, pkg.ep_plan
     ok = True
-    for T_local, E, K, d, I, beta in [(300, 32, 4, 512, 256, 0.0), (1024, 128, 8, 2048, 768, 1.0)]:
+    for T_local, E, K, d, I, beta, nmb in [(300, 32, 4, 512, 256, 0.0, 1), (300, 32, 4, 512, 256, 0.0, 2),
+                                           (1024, 128, 8, 2048, 768, 1.0, 0), (1024, 128, 8, 2048, 768, 1.0, 2)]:
         cfg = dataclasses.replace(synth.CONFIGS["c1"], T=T_local * world, E=E, K=K, d=d, I=I, zipf_beta=beta)
         inp = synth.layer_inputs(cfg, 7)
         full = O.layer(inp.proj, inp.x16, inp.wgu, inp.wdown, K)
@@ -30,33 +31,36 @@ def main():
         lo, hi = rank * T_local, (rank + 1) * T_local
         uid = [mc.ep_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
+        eff_mb = nmb if nmb else (2 if world >= 4 else 1)
+        r0 = T_local if eff_mb == 1 else min(T_local, ((T_local + 1) // 2 + 7) // 8 * 8)
+        # expected rows: inside the owner's buffer of the token's micro-batch, rows of an expert are ordered
+        # (source rank, token) -- the single-device order restricted to that micro-batch
+        want = np.empty((T_local, K), np.int64)
+        for m, (a, b) in enumerate([(0, r0), (r0, T_local)][:eff_mb]):
+            cnt_m = np.stack([np.bincount(full.idx[r * T_local + a:r * T_local + b].ravel(), minlength=E)
+                              for r in range(world)]).astype(np.uint32)
+            dst_off = epp.plan(cnt_m, rank)[0]
+            mine = full.idx[lo + a:lo + b]
+            want[a:b] = dst_off[mine].astype(np.int64) + epp.local_ranks(mine)
         with mc.Ctx(local) as ctx:
-            ctx.ep_init(uid[0], rank, world, E, K, d, I, T_local)
+            ctx.ep_init(uid[0], rank, world, E, K, d, I, T_local, nmb)
             d_proj, d_x = ctx.upload(np.ascontiguousarray(inp.proj[lo:hi])), ctx.upload(np.ascontiguousarray(inp.x16[lo:hi]))
             d_wgu = ctx.upload(np.ascontiguousarray(inp.wgu[rank * el:(rank + 1) * el]))
             d_wdown = ctx.upload(np.ascontiguousarray(inp.wdown[rank * el:(rank + 1) * el]))
             d_idx, d_slot, d_wt = ctx.alloc(T_local * K * 4), ctx.alloc(T_local * K * 4), ctx.alloc(T_local * K * 4)
-            d_off = ctx.alloc(E * 4)
             for rep in range(2):    # the second pass reuses the peer buffers
                 d_h = ctx.zeros(T_local * d * 4)
                 ctx.ep_layer(rows=T_local, d=d, experts=E, topk=K, inter=I, shared=0, pstride=cfg.pstride, hc=1,
-                             proj=d_proj, x16=d_x, wgu=d_wgu, wdown=d_wdown, h=d_h, idx=d_idx, slot=d_slot,
-                             wt=d_wt, off=d_off)
+                             proj=d_proj, x16=d_x, wgu=d_wgu, wdown=d_wdown, h=d_h, idx=d_idx, slot=d_slot, wt=d_wt)
                 ctx.flush()
                 idx = d_idx.read(np.uint32, (T_local, K))
                 slot = d_slot.read(np.uint32, (T_local, K))
                 h = d_h.read(np.float32, (T_local, d))
-                # expected rows: single-device slot, rebased from the global to the owner's offsets
-                cnt_all = np.stack([np.bincount(full.idx[r * T_local:(r + 1) * T_local].ravel(), minlength=E)
-                                    for r in range(world)]).astype(np.uint32)
-                off_owner = np.concatenate([epp.plan(cnt_all, o)[1] for o in range(world)])
-                want = full.slot[lo:hi].astype(np.int64) - full.off[idx] + off_owner[idx]
                 err = np.abs(h - full.h[lo:hi, 0])
                 good = (np.array_equal(idx, full.idx[lo:hi]) and np.array_equal(slot, want)
-                        and np.array_equal(d_off.read(np.uint32, (E,)), epp.plan(cnt_all, rank)[0])
                         and bool(np.all(err <= 1e-3 + 2e-2 * np.abs(full.h[lo:hi, 0]))))
                 if not good:
-                    print(f"rank {rank}: mismatch T{T_local} E{E} rep{rep}: idx {np.array_equal(idx, full.idx[lo:hi])} "
+                    print(f"rank {rank}: mismatch T{T_local} E{E} mb{nmb} rep{rep}: idx {np.array_equal(idx, full.idx[lo:hi])} "
                           f"slot {np.array_equal(slot, want)} max err {err.max():.3e}", flush=True)
                 ok = ok and good
             dist.barrier()
