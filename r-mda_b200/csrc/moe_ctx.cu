@@ -273,7 +273,7 @@ extern "C" void moe_cuda_prof_read(moe_cuda_ctx_t *c, float ms[MOE_PROF_STAGES])
     }
 }
 
-// 2-D fp16 tensor map [rows x cols], row-major, 128-byte swizzle, zero fill
+// 2-D fp16 tensor map [rows x cols], row-major, swizzle = the box's row width (128 or 64 bytes), zero fill
 // outside the tensor; never multicast.  Cached per (pointer, shape, box).
 typedef CUresult (*moe_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
@@ -289,7 +289,7 @@ const CUtensorMap *moe_tmap_2d_f16(moe_cuda_ctx *c, const void *ptr, uint64_t ro
             return &t->map;
         }
     }
-    if (((uintptr_t)ptr & 15) != 0 || (cols * 2) % 16 != 0 || box_cols * 2 != 128 || box_rows > 256 || rows == 0) {
+    if (((uintptr_t)ptr & 15) != 0 || (cols * 2) % 16 != 0 || (box_cols * 2 != 128 && box_cols * 2 != 64) || box_rows > 256 || rows == 0) {
         moe_fail(c, MOE_ERR_ARG, "tensor map: base %p rows %llu cols %llu not TMA-addressable", ptr,
                  (unsigned long long)rows, (unsigned long long)cols);
         return NULL;
@@ -302,7 +302,8 @@ const CUtensorMap *moe_tmap_2d_f16(moe_cuda_ctx *c, const void *ptr, uint64_t ro
     cuuint32_t estr[2] = {1, 1};
     CUresult r = ((moe_encode_fn)c->encode_tiled)(&t->map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)ptr, dims,
                                                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                  box_cols * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         moe_fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled failed: %d", (int)r);

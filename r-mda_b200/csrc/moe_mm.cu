@@ -23,9 +23,16 @@ namespace {
 
 using namespace moe_tc;
 
-constexpr uint32_t BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr uint32_t A_BYTES = BM * BK * 2;       // 16 KB
-constexpr uint32_t BH_BYTES = 128 * BK * 2;     // 16 KB: half of the B tile
+#ifndef MM_BK
+#define MM_BK 64
+#endif
+// K step per stage: 64 (128-byte rows, 128-byte swizzle, 4 stages of 48 KB).  32 (64-byte rows, 64-byte
+// swizzle, 8 stages of 24 KB) also builds and passes the parity tests but is 40 % slower on B200: its
+// half-line row requests stream worse, which outweighs the finer stage recycling.
+constexpr uint32_t BM = 128, BN = 256, BK = MM_BK, STAGES = 256 / MM_BK;
+constexpr uint32_t ROW_BYTES = BK * 2;          // bytes of one operand row per stage = the swizzle span
+constexpr uint32_t A_BYTES = BM * BK * 2;
+constexpr uint32_t BH_BYTES = 128 * BK * 2;     // half of the B tile
 constexpr uint32_t STAGE_BYTES = A_BYTES + 2 * BH_BYTES;
 constexpr uint32_t MM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
@@ -187,7 +194,8 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     if (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     tc_fence_after();
                     uint32_t base = stage0 + s * STAGE_BYTES;
-                    uint64_t ad = umma_desc(base), bd = umma_desc(base + A_BYTES);
+                    uint64_t ad = BK == 64 ? umma_desc(base) : umma_desc_sw64(base);
+                    uint64_t bd = BK == 64 ? umma_desc(base + A_BYTES) : umma_desc_sw64(base + A_BYTES);
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
                         // +32 bytes per K=16 step inside the 128-byte swizzle row
@@ -207,11 +215,14 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         __syncwarp();
     } else if (GATHER && warp >= 6) {
         // ---------------- row gather (warps 6..9) ----------------
-        // Thread g of the 128 handles 16-byte chunk (g & 7) of rows (g >> 3) + 16 j, j < 8: eight
-        // consecutive lanes fetch one whole 128-byte line of a row, so every request is a full line.
+        // CPR = 16-byte chunks per operand row and stage.  Thread g of the 128 handles chunk g % CPR of rows
+        // g / CPR + RPI * j: consecutive lanes fetch consecutive chunks of a row, so requests are whole
+        // 64- or 128-byte pieces of a line.
+        constexpr uint32_t CPR = ROW_BYTES / 16u, RPI = 128u / CPR, NJ = BM / RPI;
         const uint32_t g = (warp - 6u) * 32u + lane;
-        const uint32_t sub = g >> 3, ch = g & 7u;
-        const uint32_t dst_off = sub * 128u + ((ch ^ (sub & 7u)) << 4);  // 128-byte swizzle: chunk ^ (row % 8)
+        const uint32_t sub = g / CPR, ch = g % CPR;
+        // swizzle as TMA writes it: 128-byte rows: chunk ^ (row % 8); 64-byte rows: chunk ^ ((row / 2) % 4)
+        const uint32_t dst_off = sub * ROW_BYTES + ((ch ^ (BK == 64 ? (sub & 7u) : ((sub >> 1) & 3u))) << 4);
         uint32_t s = 0, ph = 0;
         bool ok = true;
         for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
@@ -220,11 +231,11 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 if (a.prefix) break;
                 continue;
             }
-            const __half *rowp[8];
+            const __half *rowp[NJ];
             uint32_t live = 0;
 #pragma unroll
-            for (uint32_t j = 0; j < 8; j += 1) {
-                const uint32_t src = a.src_row[it.mt * BM + j * 16u + sub];
+            for (uint32_t j = 0; j < NJ; j += 1) {
+                const uint32_t src = a.src_row[it.mt * BM + j * RPI + sub];
                 rowp[j] = a.X + (size_t)(src == ~0u ? 0u : src) * a.ldx + ch * 8u;
                 live |= (src != ~0u ? 1u : 0u) << j;
             }
@@ -239,9 +250,9 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 const uint32_t dst = stage0 + s * STAGE_BYTES + dst_off;
                 const uint32_t col = kb * BK + ch * 8u;
 #pragma unroll
-                for (uint32_t j = 0; j < 8; j += 1) {
+                for (uint32_t j = 0; j < NJ; j += 1) {
                     const uint32_t nbytes = (((live >> j) & 1u) != 0u && col < a.k) ? 16u : 0u;  // 0: zero-filled
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + j * 16u * 128u),
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + j * RPI * ROW_BYTES),
                                  "l"(rowp[j] + (nbytes != 0u ? kb * BK : 0u)), "r"(nbytes)
                                  : "memory");
                 }
