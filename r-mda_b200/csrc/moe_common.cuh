@@ -49,6 +49,7 @@ struct moe_cuda_ctx {
     uint64_t launches;
     int fail_alloc_countdown;
     bool mm_attr_set[4];
+    uint32_t *ticket;  // device word, zero between kernels: "last block done" counter
     bool sw_attr_set[8];
     moe_ep_state *ep;
 };
@@ -96,9 +97,13 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
                         uint32_t d8, uint32_t experts_bound, void *const *xp_peers = NULL,
                         uint32_t experts_per_rank = 0);
 
+// ones_a / ones_b: up to two word tables the router also fills with ~0 (tile schedule, source rows).
 void moe_launch_route_hist(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *wt, uint32_t *hist,
-                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride);
-void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts);
+                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride, uint32_t *ones_a = NULL,
+                           uint32_t n_a = 0, uint32_t *ones_b = NULL, uint32_t n_b = 0);
+// off / tiles non-NULL: the last block to finish also runs the reference's scan on the fresh counts.
+void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts,
+                               uint32_t *off = NULL, uint32_t *tiles = NULL, uint32_t tile = 0);
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
                       void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row = NULL);
@@ -142,6 +147,40 @@ struct moe_combine_args {
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a);
 
 // ---- device helpers -------------------------------------------------------
+// shader/moe_scan.comp:14-38, for a block of at least 512 threads (all threads of the block must
+// call it; thread e < 512 handles expert e).  count is read past L1.
+__device__ __forceinline__ void moe_scan_body(const uint32_t *count, uint32_t *off, uint32_t *tiles, uint32_t experts,
+                                              uint32_t tile) {
+    __shared__ uint32_t wsum[16];
+    const uint32_t e = threadIdx.x;
+    const uint32_t lane = e & 31u, warp = e >> 5;
+    uint32_t p = 0;
+    if (e < experts) p = (__ldcg(count + e) + tile - 1u) / tile * tile;  // :19
+    uint32_t incl = p;
+#pragma unroll
+    for (uint32_t o = 1; o < 32; o <<= 1) {
+        uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31 && warp < 16) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t w = lane < 16 ? wsum[lane] : 0;
+#pragma unroll
+        for (uint32_t o = 1; o < 16; o <<= 1) {
+            uint32_t v = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += v;
+        }
+        if (lane < 16) wsum[lane] = w;
+    }
+    __syncthreads();
+    if (e < experts) {
+        uint32_t lo = incl - p + (warp > 0 ? wsum[warp - 1] : 0);  // :31
+        off[e] = lo;                                                // :33
+        for (uint32_t t = lo / tile; t < (lo + p) / tile; t += 1) tiles[t] = e;  // :34-36
+    }
+}
+
 __device__ __forceinline__ float moe_slot_scale(const uint32_t *amax, uint32_t s) {
     // shader/matmul_f16_moe.comp:60-68 = shader/cast_f16.comp:20-28
     if (s == MDA_PC_NO_SLOT) return 1.0f;

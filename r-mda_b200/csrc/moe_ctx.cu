@@ -95,6 +95,7 @@ extern "C" void moe_cuda_destroy(moe_cuda_ctx_t *c) {
     if (c->ev_made) {
         for (int i = 0; i <= MOE_PROF_STAGES; i += 1) cudaEventDestroy(c->ev[i]);
     }
+    if (c->ticket != NULL) cudaFree(c->ticket);
     if (c->dev_status_host != NULL) cudaFreeHost(c->dev_status_host);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     free(c);

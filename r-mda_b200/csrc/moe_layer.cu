@@ -107,8 +107,8 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
 
     mark(c, 0);
     // src/qwen.c:793-798
-    moe_cuda_fill(c, tiles, (size_t)(M / MOE_TILE) * 4, 0xffffffffu);
     if (unfused) {
+        moe_cuda_fill(c, tiles, (size_t)(M / MOE_TILE) * 4, 0xffffffffu);
         moe_cuda_fill(c, count, (size_t)E * 4, 0);
         moe_cuda_fill(c, b.fill, (size_t)E * 4, 0);
         moe_cuda_fill(c, b.xp, (size_t)M * d * 2, 0);
@@ -126,12 +126,12 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
         // the stable ranking.
         uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)((R + 7u) / 8u) * E * 4);
         if (hist == NULL) return;
-        moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride);
+        // the router also fills the tile schedule and (gather mode) the source-row table with ~0
+        moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride, tiles, M / MOE_TILE,
+                              gather ? b.src_row : NULL, gather ? M : 0u);
         mark(c, 1);
-        moe_launch_colscan_counts(c, hist, count, R, E);
-        moe_launch_scan(c, count, off, tiles, E, MOE_TILE);
+        moe_launch_colscan_counts(c, hist, count, R, E, off, tiles, MOE_TILE);  // + the scan, in its last block
         mark(c, 2);
-        if (gather) moe_cuda_fill(c, b.src_row, (size_t)M * 4, 0xffffffffu);  // padding rows read as zero
         moe_launch_place(c, idx, off, hist, L->x16, b.xp, slot, R, K, d / 8u, E, NULL, 0, gather ? b.src_row : NULL);
     }
     mark(c, 3);

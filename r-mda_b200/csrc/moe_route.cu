@@ -20,8 +20,14 @@ template <bool HIST, int NB>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float *__restrict__ proj, uint32_t *__restrict__ idx, float *__restrict__ wt,
                  uint32_t *__restrict__ count, uint32_t rows, uint32_t experts, uint32_t topk,
-                 uint32_t stride, uint32_t *status, int vec_ok) {
+                 uint32_t stride, uint32_t *status, int vec_ok, uint32_t *__restrict__ ones_a, uint32_t n_a,
+                 uint32_t *__restrict__ ones_b, uint32_t n_b) {
     __shared__ uint32_t s_hist[HIST ? MOE_MAX_EXPERTS : 1];
+    if (HIST) {
+        // the fills of src/qwen.c:796 ride along: tables that later kernels expect to start as ~0
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_a; i += gridDim.x * blockDim.x) ones_a[i] = ~0u;
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_b; i += gridDim.x * blockDim.x) ones_b[i] = ~0u;
+    }
     uint32_t lane = threadIdx.x & 31u;
     uint32_t warp = threadIdx.x >> 5;
     uint32_t nwarps = gridDim.x * ROUTE_WARPS;
@@ -111,13 +117,16 @@ moe_route_kernel(const float *__restrict__ proj, uint32_t *__restrict__ idx, flo
 
 template <bool HIST>
 static void route_dispatch(moe_cuda_ctx *c, uint32_t blocks, const float *proj, uint32_t *idx, float *wt, uint32_t *count,
-                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride, int vec_ok) {
+                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride, int vec_ok,
+                           uint32_t *ones_a = NULL, uint32_t n_a = 0, uint32_t *ones_b = NULL, uint32_t n_b = 0) {
     const uint32_t nb = (experts + 127u) / 128u;
     const dim3 g(blocks), t(ROUTE_WARPS * 32);
-    if (nb == 1) moe_route_kernel<HIST, 1><<<g, t, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok);
-    else if (nb == 2) moe_route_kernel<HIST, 2><<<g, t, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok);
-    else if (nb == 3) moe_route_kernel<HIST, 3><<<g, t, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok);
-    else moe_route_kernel<HIST, 4><<<g, t, 0, c->stream>>>(proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok);
+#define ROUTE_ARGS proj, idx, wt, count, rows, experts, topk, stride, c->dev_status_dev, vec_ok, ones_a, n_a, ones_b, n_b
+    if (nb == 1) moe_route_kernel<HIST, 1><<<g, t, 0, c->stream>>>(ROUTE_ARGS);
+    else if (nb == 2) moe_route_kernel<HIST, 2><<<g, t, 0, c->stream>>>(ROUTE_ARGS);
+    else if (nb == 3) moe_route_kernel<HIST, 3><<<g, t, 0, c->stream>>>(ROUTE_ARGS);
+    else moe_route_kernel<HIST, 4><<<g, t, 0, c->stream>>>(ROUTE_ARGS);
+#undef ROUTE_ARGS
     MOE_LAUNCHED(c);
 }
 
@@ -139,7 +148,8 @@ void moe_launch_route(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *
 // Fused-layer front end: routing plus the per-block expert table of the scatter
 // (block = 8 consecutive rows = 8*topk pairs).  hist has ceil(rows/8) x experts words.
 void moe_launch_route_hist(moe_cuda_ctx *c, const float *proj, uint32_t *idx, float *wt, uint32_t *hist,
-                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride) {
+                           uint32_t rows, uint32_t experts, uint32_t topk, uint32_t stride, uint32_t *ones_a,
+                           uint32_t n_a, uint32_t *ones_b, uint32_t n_b) {
     if (!MOE_LIVE(c)) return;
     MOE_REQUIRE(c, experts >= 1 && experts <= MOE_MAX_EXPERTS, "route: experts %u outside 1..512", experts);
     MOE_REQUIRE(c, topk >= 1 && topk <= MOE_MAX_TOPK && topk <= experts, "route: topk %u outside 1..min(16, experts)", topk);
@@ -148,7 +158,7 @@ void moe_launch_route_hist(moe_cuda_ctx *c, const float *proj, uint32_t *idx, fl
     if (rows == 0) return;
     int vec_ok = ((uintptr_t)proj % 16 == 0) && (stride % 4 == 0);
     uint32_t blocks = (rows + ROUTE_WARPS - 1) / ROUTE_WARPS;  // exactly one block per 8 rows: no grid stride
-    route_dispatch<true>(c, blocks, proj, idx, wt, hist, rows, experts, topk, stride, vec_ok);
+    route_dispatch<true>(c, blocks, proj, idx, wt, hist, rows, experts, topk, stride, vec_ok, ones_a, n_a, ones_b, n_b);
 }
 
 extern "C" void moe_cuda_route(moe_cuda_ctx_t *c, const float *proj, uint32_t *idx, float *wt, uint32_t *count,
@@ -157,38 +167,11 @@ extern "C" void moe_cuda_route(moe_cuda_ctx_t *c, const float *proj, uint32_t *i
 }
 
 // shader/moe_scan.comp:14-38: one 512-thread block; pad each count to the tile,
-// exclusive prefix sum, one tiles[] entry per padded tile.
+// exclusive prefix sum, one tiles[] entry per padded tile (moe_scan_body, moe_common.cuh).
 __global__ void __launch_bounds__(512)
 moe_scan_kernel(const uint32_t *__restrict__ count, uint32_t *__restrict__ off, uint32_t *__restrict__ tiles,
                 uint32_t experts, uint32_t tile) {
-    __shared__ uint32_t wsum[16];
-    uint32_t e = threadIdx.x;
-    uint32_t lane = e & 31u, warp = e >> 5;
-    uint32_t p = 0;
-    if (e < experts) p = (count[e] + tile - 1u) / tile * tile;  // :19
-    uint32_t incl = p;
-#pragma unroll
-    for (uint32_t o = 1; o < 32; o <<= 1) {
-        uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-    }
-    if (lane == 31) wsum[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-        uint32_t w = lane < 16 ? wsum[lane] : 0;
-#pragma unroll
-        for (uint32_t o = 1; o < 16; o <<= 1) {
-            uint32_t v = __shfl_up_sync(0xffffffffu, w, o);
-            if (lane >= o) w += v;
-        }
-        if (lane < 16) wsum[lane] = w;
-    }
-    __syncthreads();
-    uint32_t lo = incl - p + (warp > 0 ? wsum[warp - 1] : 0);  // :31
-    if (e < experts) {
-        off[e] = lo;  // :33
-        for (uint32_t t = lo / tile; t < (lo + p) / tile; t += 1) tiles[t] = e;  // :34-36
-    }
+    moe_scan_body(count, off, tiles, experts, tile);
 }
 
 void moe_launch_scan(moe_cuda_ctx *c, const uint32_t *count, uint32_t *off, uint32_t *tiles, uint32_t experts,

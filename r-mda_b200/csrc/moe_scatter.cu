@@ -43,8 +43,10 @@ moe_scatter_hist_kernel(const uint32_t *__restrict__ idx, uint32_t *__restrict__
 #define CS_EXPERTS 32u
 __global__ void __launch_bounds__(1024)
 moe_scatter_colscan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fill, uint32_t nblocks,
-                           uint32_t ebound, uint32_t *__restrict__ count_out) {
+                           uint32_t ebound, uint32_t *__restrict__ count_out, uint32_t *ticket, uint32_t *off,
+                           uint32_t *tiles, uint32_t tile) {
     __shared__ uint32_t seg_sum[32][33];
+    __shared__ uint32_t s_last;
     uint32_t el = threadIdx.x & 31u, seg = threadIdx.x >> 5;
     uint32_t e = blockIdx.x * 32u + el;
     uint32_t per = (nblocks + 31u) / 32u;
@@ -86,6 +88,20 @@ moe_scatter_colscan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ f
         if (seg == 31) {
             if (fill != NULL) fill[e] += run;          // state after the shader's atomics (:25)
             if (count_out != NULL) count_out[e] = run;  // per-expert totals double as the router's counts
+        }
+    }
+    if (ticket != NULL) {
+        // the block that finishes last sees every count and runs the scan (shader/moe_scan.comp) right here
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            s_last = atomicAdd(ticket, 1u) == gridDim.x - 1u ? 1u : 0u;
+            if (s_last) *ticket = 0;  // ready for the next launch
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            moe_scan_body(count_out, off, tiles, ebound, tile);
         }
     }
 }
@@ -158,7 +174,7 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
     moe_scatter_hist_kernel<<<nblocks, SC_PAIRS, ebound * sizeof(uint32_t), c->stream>>>(idx, hist, pairs, ebound,
                                                                                          c->dev_status_dev);
     MOE_LAUNCHED(c);
-    moe_scatter_colscan_kernel<<<(ebound + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, fill, nblocks, ebound, NULL);
+    moe_scatter_colscan_kernel<<<(ebound + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, fill, nblocks, ebound, NULL, NULL, NULL, NULL, 0);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp,
                                                                     slot, pairs, topk, d8, ebound,
@@ -168,11 +184,22 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
 
 // Fused front end, after the router wrote the per-8-row tables into `hist`:
 // column scan in place (block bases for the ranking) which also yields count[].
-void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts) {
+void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts,
+                               uint32_t *off, uint32_t *tiles, uint32_t tile) {
     if (!MOE_LIVE(c)) return;
     if (rows == 0) return;
     uint32_t nblocks = (rows + 7u) / 8u;
-    moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, NULL, nblocks, experts, count);
+    uint32_t *ticket = NULL;
+    if (off != NULL) {
+        if (c->ticket == NULL) {
+            c->ticket = (uint32_t *)moe_cuda_alloc(c, 64);
+            if (c->ticket == NULL) return;
+            MOE_CUDA_TRY(c, cudaMemsetAsync(c->ticket, 0, 64, c->stream));
+        }
+        ticket = c->ticket;
+    }
+    moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, NULL, nblocks, experts, count,
+                                                                                                 ticket, off, tiles, tile);
     MOE_LAUNCHED(c);
 }
 
@@ -246,7 +273,7 @@ extern "C" void moe_cuda_scatter_noalloc(moe_cuda_ctx_t *c, const uint32_t *idx,
     moe_scatter_hist_kernel<<<(uint32_t)nblocks, SC_PAIRS, experts * sizeof(uint32_t), c->stream>>>(
         idx, table, (uint32_t)pairs, experts, c->dev_status_dev);
     MOE_LAUNCHED(c);
-    moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts, NULL);
+    moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts, NULL, NULL, NULL, NULL, 0);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<(uint32_t)nblocks, SC_THREADS, 0, c->stream>>>(
         idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0, SC_PAIRS, NULL);
