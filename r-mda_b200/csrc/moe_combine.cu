@@ -116,6 +116,16 @@ moe_combine_kernel(moe_combine_args a) {
     }
 }
 
+// Lets the kernels that move rows over NVLink share an SM with a resident grouped-product CTA: a
+// kernel can only join an SM whose shared-memory carve-out matches its own, and the products run
+// with the maximum carve-out.
+void moe_overlap_prepare_combine(moe_cuda_ctx *c) {
+    MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_combine_kernel<__half, false, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
+    MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_combine_kernel<__half, true, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
+}
+
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a) {
     if (!MOE_LIVE(c)) return;
     MOE_REQUIRE(c, a.wt != NULL && a.slot != NULL && (a.y != NULL || a.y_peers != NULL), "combine: null buffer");

@@ -145,6 +145,8 @@ struct moe_combine_args {
     uint32_t experts_per_rank;
 };
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a);
+void moe_overlap_prepare_combine(moe_cuda_ctx *c);
+void moe_overlap_prepare_scatter(moe_cuda_ctx *c);
 
 // ---- device helpers -------------------------------------------------------
 // shader/moe_scan.comp:14-38, for a block of at least 512 threads (all threads of the block must

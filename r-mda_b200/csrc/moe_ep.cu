@@ -154,6 +154,12 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
     c->ep = NULL;
 }
 
+__global__ void moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t world, uint32_t rank, uint32_t site, uint32_t epoch,
+                                      uint32_t *status);
+__global__ void moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch, uint32_t site,
+                                   uint32_t table_off, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
+                                   uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status);
+
 // Joins the communicator, allocates the peer-visible buffers for the stated
 // maximum shape and maps every peer's buffers.  Collective over all ranks.
 extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, int rank, int world,
@@ -214,6 +220,12 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     ep->bar = (uint32_t *)moe_cuda_alloc(c, 256);
     if (c->status != MOE_OK) return;
     if (nmb > 1) {
+        // the transfer kernels of one slice must be able to run on SMs that hold a product CTA of the other
+        moe_overlap_prepare_combine(c);
+        moe_overlap_prepare_scatter(c);
+        MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_barrier_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_plan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        if (c->status != MOE_OK) return;
         MOE_CUDA_TRY(c, cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking));
         MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_fork, cudaEventDisableTiming));
         MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_disp, cudaEventDisableTiming));

@@ -203,6 +203,13 @@ void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count,
     MOE_LAUNCHED(c);
 }
 
+void moe_overlap_prepare_scatter(moe_cuda_ctx *c) {
+    MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_scatter_place_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
+    MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_scatter_colscan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
+}
+
 // Ranking + row copies for blocks of 8 rows (8*topk pairs), bases from `hist`.
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,

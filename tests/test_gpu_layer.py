@@ -87,3 +87,37 @@ def test_shared_expert_small(ctx, mc, synth, oracle):
     ref = oracle.layer(inp.proj, inp.x16, inp.wgu, inp.wdown, cfg.K, inp.wsgu, inp.wsdown)
     check(run_layer(ctx, mc, cfg, inp, 0), ref)
     check(run_layer(ctx, mc, cfg, inp, 1), ref)
+
+
+def test_upstream_projection_on_gpu_then_layer(ctx, mc, synth, oracle):
+    """The product just upstream of the path (src/qwen.c:845: router logits, shared-gate logit and the
+    padding columns in one fp16 product with fp32 output) runs on the same grouped kernel with a
+    single "expert"; the layer then routes on those GPU logits and the oracle re-routes on the
+    same downloaded values, so both sides see bit-identical router inputs."""
+    import dataclasses
+    cfg = dataclasses.replace(synth.CONFIGS["c1"], T=640, E=128, name="c1-T640")
+    inp = synth.layer_inputs(cfg, 4)
+    wr, wsg = synth.router_weights(cfg, 4)
+    T, d, pcols = cfg.T, cfg.d, cfg.pstride                      # E + 128 columns, a multiple of 128
+    wd = np.zeros((1, pcols, d), np.float16)                     # packed like mda_qwen_put_moe (src/qwen.c:441-452)
+    wd[0, :cfg.E] = wr.astype(np.float16)
+    wd[0, cfg.E] = wsg.astype(np.float16)
+    wd16 = wd.view(np.uint16)
+    tiles0 = np.zeros(T // 128, np.uint32)
+    ref_proj = oracle.mm(inp.x16, wd16, tiles0, pcols, d)
+    d_x, d_proj = ctx.upload(inp.x16), ctx.alloc(T * pcols * 4)
+    ctx.mm(d_x, ctx.upload(wd16), d_proj, None, ctx.upload(tiles0), T, pcols, d, experts_in_B=1)
+    ctx.flush()
+    proj = d_proj.read(np.float32, (T, pcols))
+    assert np.allclose(proj, ref_proj, rtol=1e-3, atol=1e-4)
+    assert np.abs(proj - inp.proj).max() < 0.05                  # fp16 router weights move the logits only slightly
+    ref = oracle.layer(proj, inp.x16, inp.wgu, inp.wdown, cfg.K)  # the oracle routes on the GPU's logits
+    d_h = ctx.zeros(T * d * 4)
+    d_idx, d_slot = ctx.alloc(T * cfg.K * 4), ctx.alloc(T * cfg.K * 4)
+    ctx.layer(rows=T, d=d, experts=cfg.E, topk=cfg.K, inter=cfg.I, shared=0, pstride=pcols, hc=1, proj=d_proj, x16=d_x,
+              wgu=ctx.upload(inp.wgu), wdown=ctx.upload(inp.wdown), h=d_h, idx=d_idx, slot=d_slot)
+    ctx.flush()
+    assert np.array_equal(d_idx.read(np.uint32, (T, cfg.K)), ref.idx)
+    assert np.array_equal(d_slot.read(np.uint32, (T, cfg.K)), ref.slot)
+    h = d_h.read(np.float32, (T, 1, d))
+    assert np.all(np.abs(h - ref.h) <= ATOL_OUT + RTOL_OUT * np.abs(ref.h))
