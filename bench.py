@@ -32,7 +32,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, the
 # gate_up grouped product with row gather, at the 30B-A3B shape, from the Nsight Compute capture
 # summarised in profiles/moe_mm_kernel_30B-A3B.md (full-size launch, no scaling involved).
-NCU_TRAFFIC_BYTES = {"c1": 913420800 + 59392000}
+NCU_TRAFFIC_BYTES = {"c1": 883223040 + 58677504}
 
 
 def peaks():
