@@ -183,6 +183,9 @@ def run_ours(args):
         from bench_ep import run_ep  # noqa: F401  (expert-parallel driver)
         return run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local)
 
+    if cfg.layers > 1:
+        return run_stack(args, ctx, mc, synth, cfg, stream, local)
+
     inp = synth.layer_inputs(cfg, 0)
     d_wgu, d_wdown = ctx.upload(inp.wgu), ctx.upload(inp.wdown)
     d_wsgu = ctx.upload(inp.wsgu) if cfg.S else None
@@ -323,13 +326,105 @@ def emit(args, out):
     print(json.dumps(out), flush=True)
 
 
+def run_stack(args, ctx, mc, synth, cfg, stream, local):
+    """Config 4: the teacher-forward stack -- `layers` MoE layers of the 30B-A3B shape back to back
+    on T=4096 tokens, each with its own seeded weights resident in HBM, each followed by a residual
+    add and RMSNorm (eps 1e-6, fused into the combine).  Because the activations change from layer
+    to layer, the upstream projection (router logits, src/qwen.c:845) runs on the GPU too, on the
+    grouped kernel with one "expert"; it is timed as part of the step.  One step = one pass of the
+    whole stack."""
+    import torch
+
+    T, K, E, d, I, NL = cfg.T, cfg.K, cfg.E, cfg.d, cfg.I, cfg.layers
+    dev = torch.device("cuda", local)
+    pcols = cfg.pstride
+    gen = torch.Generator(device=dev)
+    layers = []
+    for l in range(NL):   # seeded per layer; generated on the device (58 GB of fp16 in all)
+        gen.manual_seed(1000 + l)
+        wgu = (torch.randn(E * 2 * I * d, device=dev, generator=gen, dtype=torch.float32) * 0.02).half()
+        wdown = (torch.randn(E * d * I, device=dev, generator=gen, dtype=torch.float32) * 0.02).half()
+        wd = torch.zeros(pcols * d, device=dev, dtype=torch.float16)
+        wd[:(E + 1) * d] = (torch.randn((E + 1) * d, device=dev, generator=gen, dtype=torch.float32) * 0.02).half()
+        layers.append((wgu, wdown, wd))
+    torch.cuda.synchronize()
+    x16 = synth.activations(cfg, 0)
+    d_x0 = ctx.upload(x16)
+    d_xa, d_xb = ctx.alloc(T * d * 2), ctx.alloc(T * d * 2)
+    d_proj = ctx.alloc(T * pcols * 4)
+    d_tiles0 = ctx.zeros(T // 128 * 4)
+    h_x, _ = pinned_array(mc, ctx, x16.shape, np.uint16)
+    h_y, _ = pinned_array(mc, ctx, x16.shape, np.uint16)
+    h_x[:] = x16
+    L = mc.lib()
+
+    def stack(host: bool):
+        if host:
+            L.moe_cuda_write(ctx.p, d_x0.ptr, h_x.ctypes.data, h_x.nbytes)
+        src, dst = d_x0, d_xa
+        for wgu, wdown, wd in layers:
+            ctx.mm(src, wd.data_ptr(), d_proj, None, d_tiles0, T, pcols, d, experts_in_B=1)
+            ctx.layer(rows=T, d=d, experts=E, topk=K, inter=I, shared=0, pstride=pcols, hc=1, proj=d_proj, x16=src,
+                      wgu=wgu.data_ptr(), wdown=wdown.data_ptr(), y16=dst, eps=1e-6, flags=args.flags)
+            src, dst = dst, (d_xb if dst is d_xa else d_xa)
+        if host:
+            L.moe_cuda_read(ctx.p, h_y.ctypes.data, src.ptr, h_y.nbytes)
+        return src
+
+    for _ in range(max(args.warmup, 3)):
+        stack(False)
+    ctx.flush()
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = ctx.launches()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        for _ in range(args.steps):
+            last = stack(False)
+        ev1.record(stream)
+    torch.cuda.synchronize()
+    ctx.check()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = ctx.launches() - l0
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        for _ in range(args.steps):
+            stack(True)
+        ev1.record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = ev0.elapsed_time(ev1) / args.steps
+    clocks = sampler.stop()
+    y = last.read(np.uint16, (T, d)).view(np.float16).astype(np.float32)
+    pk = peaks()
+    flops = NL * (cfg.flops() + 2 * T * pcols * d)
+    out = {
+        "metric": "teacher-forward MoE stack tokens/s (48 x [projection -> route -> grouped GEMM -> combine -> residual + RMSNorm])",
+        "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": dict(workload_config(cfg, 1), layers=NL, weights_resident_GB=round(NL * (E * 3 * d * I * 2) / 1e9, 1)),
+        "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(h_x.nbytes),
+                "d2h_bytes_per_step": int(h_y.nbytes), "ms_per_step": e2e_ms},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "per_layer_ms": ms / NL, "layer_tokens_per_s": T * NL / (ms * 1e-3),
+        "roofline": {"bound": "tensor", "kernel": "whole stack (all kernels)", "achieved": flops / (ms * 1e-3) / 1e12,
+                     "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"],
+                     "traffic": None, "peak_source": pk["source"] + " (burst)"},
+        "output_rms": float(np.sqrt((y * y).mean())),
+    }
+    ctx.close()
+    emit(args, out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c1", choices=["c0", "c1", "c2", "c3", "c3b"])
+    ap.add_argument("--config", default="c1", choices=["c0", "c1", "c2", "c3", "c3b", "c4"])
     ap.add_argument("--ref-tokens", type=int, default=1 << 30, help="tokens per CPU sample/step (default: the whole workload)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--flags", type=int, default=0, help="MOE_LAYER_* flags passed to moe_cuda_layer")

@@ -261,7 +261,7 @@ class Ctx:
 
     def layer(self, **kw):
         L = Layer()
-        for k, v in kw.items():
+        for k, v in kw.items():   # DevBuf, raw device address (int) or None for pointers; numbers otherwise
             setattr(L, k, _ptr(v) if isinstance(v, DevBuf) or v is None else v)
         lib().moe_cuda_layer(self.p, C.byref(L))
 
