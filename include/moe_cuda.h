@@ -180,8 +180,8 @@ typedef struct moe_cuda_layer_t {
 #define MOE_LAYER_UNFUSED 1u /* run the reference's kernel sequence step by step (fp32 g, absmax rescale) */
 #define MOE_LAYER_YE_F32 2u  /* keep expert outputs fp32 between the down product and the combine */
 #define MOE_LAYER_CHUNKED 4u /* experimental: weight-stationary products over per-expert token chunks (MMA width rounded to 16) instead of the reference's 128-row tile schedule */
-#define MOE_LAYER_MATERIALIZE_XP 16u /* write the permuted activations xp to HBM as the reference does, instead of letting the gate_up product gather the rows of x16 itself */
 #define MOE_LAYER_NO_PAIR 8u /* with MOE_LAYER_CHUNKED: one CTA per tile instead of tcgen05 cta_group::2 pairs */
+#define MOE_LAYER_MATERIALIZE_XP 16u /* write the permuted activations xp to HBM as the reference does, instead of letting the gate_up product gather the rows of x16 itself */
 
 /* Rows of scratch the layer needs: round128(rows*topk + experts*127), src/qwen.c:68-70. */
 uint32_t moe_cuda_moe_rows(uint32_t rows, uint32_t topk, uint32_t experts);
@@ -193,7 +193,10 @@ void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
  * One process per GPU.  Rank g owns experts [g*E/G, (g+1)*E/G) and passes only
  * their weights; every rank passes its own tokens.  Dispatch and return are
  * fused into the scatter and combine kernels as peer stores / loads over
- * NVLink; NCCL carries the per-expert counts and two barriers. */
+ * NVLink; the per-expert counts and the three rendezvous points per layer are
+ * flag exchanges over the same peer memory with bounded waits (a rank that
+ * stops coming ends the others' call with MOE_ERR_TIMEOUT after 2 s).  NCCL is
+ * needed once, at moe_cuda_ep_init, to hand round the memory handles. */
 typedef struct moe_cuda_ep_cfg_t {
     uint32_t experts, topk, d, inter; /* global expert count; experts % world == 0, inter % 128 == 0 */
     uint32_t max_rows;                /* most tokens any rank will pass in one call */
@@ -216,7 +219,9 @@ void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, int rank, int
 void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
 
 /* Per-stage device times of the last moe_cuda_layer call, in milliseconds, in
- * the order route, scan, scatter, gate_up, down, shared, combine (after
+ * the order route, scan, scatter, gate_up, down, shared, combine (for
+ * moe_cuda_ep_layer: router, counts + plan, dispatch + barrier, gate_up, down,
+ * barrier, combine + return, of the first token slice) (after
  * mda_vkc_prof_begin / prof_report, src/vkc.c:595-653).  Enabled with
  * moe_cuda_prof(c, 1); reading them synchronises the stream. */
 #define MOE_PROF_STAGES 7
