@@ -38,6 +38,7 @@ struct mda_pc_moe_combine_t { uint32_t rows, d, topk, pstride, sg_off, inj_strid
 struct mda_pc_qwen_elem_t { uint32_t rows, n, astride, ao, bo, op; float scale; };    /* shader/qwen_elem.comp:6-14 */
 struct mda_pc_absmax_t { uint32_t n, slot; };                                          /* shader/absmax.comp:6-9 */
 struct mda_pc_cast_t { uint32_t n, slot; };                                            /* shader/cast_f16.comp:14-17 */
+struct mda_pc_qwen_bf16_t { uint32_t n; };                                             /* src/pc.h:273-275 */
 #endif
 typedef struct mda_pc_moe_route_t moe_pc_route_t;
 typedef struct mda_pc_moe_scan_t moe_pc_scan_t;
@@ -152,6 +153,12 @@ void moe_cuda_swiglu(moe_cuda_ctx_t *c, const float *a, float *y, struct mda_pc_
 void moe_cuda_absmax(moe_cuda_ctx_t *c, const float *x, uint32_t *amax, struct mda_pc_absmax_t pc); /* shader/absmax.comp, src/qwen.c:858-867 */
 void moe_cuda_cast_f16(moe_cuda_ctx_t *c, const float *src, void *dst, const uint32_t *amax,
                        struct mda_pc_cast_t pc); /* shader/cast_f16.comp, src/qwen.c:868-877 */
+
+/* ---- weight upload step ---------------------------------------------------
+ * shader/qwen_bf16.comp (binding w; call mda_qwen_convert, src/qwen.c:365-378):
+ * pc.n 32-bit words of two bf16 values each, rewritten in place as fp16 (round
+ * to nearest even) right after the host-to-device copy of a layer's weights. */
+void moe_cuda_bf16_to_f16(moe_cuda_ctx_t *c, void *w, struct mda_pc_qwen_bf16_t pc);
 
 /* ---- the fused layer: mda_qwen_route_rec + mda_qwen_moe_rec from the first
  *      grouped product on (src/qwen.c:788-836, 847-906) in one call --------- */

@@ -176,6 +176,14 @@ def residual_rmsnorm(x16, delta, eps=1e-6):
     return y
 
 
+def bf16_to_f16(w):
+    """shader/qwen_bf16.comp on a copy: uint32 words of two bf16 -> two fp16."""
+    _chk(w, np.uint32, "w")
+    out = w.copy()
+    lib().moe_ref_bf16_to_f16(_p(out), C.c_uint64(out.size))
+    return out
+
+
 class _Layer(C.Structure):
     _fields_ = [
         ("rows", C.c_uint32), ("d", C.c_uint32), ("experts", C.c_uint32), ("topk", C.c_uint32),

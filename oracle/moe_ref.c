@@ -282,6 +282,19 @@ void moe_ref_residual_rmsnorm(const uint16_t *x16, const float *delta, uint16_t 
     }
 }
 
+/* shader/qwen_bf16.comp:9-15: u -> packHalf2x16(float(lo bf16), float(hi bf16)). */
+void moe_ref_bf16_to_f16(uint32_t *w, uint64_t n) {
+#pragma omp parallel for schedule(static)
+    for (uint64_t i = 0; i < n; i += 1) {
+        uint32_t u = w[i];
+        uint32_t lo_bits = u << 16, hi_bits = u & 0xffff0000u;
+        float lo, hi;
+        memcpy(&lo, &lo_bits, 4);
+        memcpy(&hi, &hi_bits, 4);
+        w[i] = (uint32_t)moe_ref_f2h(lo) | ((uint32_t)moe_ref_f2h(hi) << 16);
+    }
+}
+
 /* src/qwen.c:788-836 (mda_qwen_route_rec) then src/qwen.c:847-906
  * (mda_qwen_moe_rec from the first grouped product on). */
 int moe_ref_layer(moe_ref_layer_t *L) {

@@ -85,6 +85,11 @@ void moe_ref_combine(const float *wt, const uint32_t *slot, const float *y, cons
 void moe_ref_residual_rmsnorm(const uint16_t *x16, const float *delta, uint16_t *y16,
                               uint32_t rows, uint32_t d, float eps);
 
+/* shader/qwen_bf16.comp:9-15 (call src/qwen.c:365-378): n 32-bit words, each two
+ * bf16 values, rewritten in place as two fp16 values (round to nearest even,
+ * overflow to infinity), as the upload of a layer's weights does. */
+void moe_ref_bf16_to_f16(uint32_t *w, uint64_t n);
+
 /* One whole layer in the order of src/qwen.c:788-907 (mda_qwen_route_rec then
  * mda_qwen_moe_rec from the first grouped product on).  All buffers are
  * caller-owned; see moe_ref_layer_t. */

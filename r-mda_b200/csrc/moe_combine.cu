@@ -250,3 +250,38 @@ extern "C" void moe_cuda_cast_f16(moe_cuda_ctx_t *c, const float *src, void *dst
     moe_cast_f16_kernel<<<blocks, 256, 0, c->stream>>>(src, (__half *)dst, pc.n, amax, pc.slot);
     MOE_LAUNCHED(c);
 }
+
+// ---- weight upload step: shader/qwen_bf16.comp (call src/qwen.c:365-378) ----
+// The reference uploads a layer's bf16 weights and rewrites them in place as fp16 on the
+// device.  HBM bound (2 bytes read + 2 bytes written per value): 128-bit accesses, grid-stride.
+__device__ __forceinline__ uint32_t moe_bf16x2_to_f16x2(uint32_t u) {
+    __half2 h = __floats2half2_rn(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));  // qwen_bf16.comp:13
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+__global__ void moe_bf16_to_f16_kernel(uint32_t *__restrict__ w, size_t n) {
+    size_t n4 = n / 4;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    uint4 *w4 = reinterpret_cast<uint4 *>(w);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        uint4 v = w4[i];
+        v.x = moe_bf16x2_to_f16x2(v.x);
+        v.y = moe_bf16x2_to_f16x2(v.y);
+        v.z = moe_bf16x2_to_f16x2(v.z);
+        v.w = moe_bf16x2_to_f16x2(v.w);
+        w4[i] = v;
+    }
+    size_t tail = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tail < n) w[tail] = moe_bf16x2_to_f16x2(w[tail]);
+}
+
+extern "C" void moe_cuda_bf16_to_f16(moe_cuda_ctx_t *c, void *w, struct mda_pc_qwen_bf16_t pc) {
+    if (!MOE_LIVE(c)) return;
+    MOE_REQUIRE(c, w != NULL && ((uintptr_t)w & 15) == 0, "bf16_to_f16: null or unaligned buffer");
+    if (pc.n == 0) return;
+    size_t blocks = ((size_t)pc.n / 4 + 255) / 256;
+    if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
+    if (blocks == 0) blocks = 1;
+    moe_bf16_to_f16_kernel<<<(unsigned)blocks, 256, 0, c->stream>>>((uint32_t *)w, pc.n);
+    MOE_LAUNCHED(c);
+}

@@ -88,6 +88,17 @@ uint32_t moe_host_slot(moe_host_t *q) { /* src/qwen.c:505-515 */
     }
 }
 
+/* mda_qwen_convert, src/qwen.c:365-378: bf16 -> fp16 in place after the upload */
+void moe_host_convert(moe_host_t *q, void *dev, uint64_t used_bytes) {
+    uint32_t n = (uint32_t)(used_bytes / sizeof(uint32_t));
+    if (n > 0) {
+        struct mda_pc_qwen_bf16_t pc = {
+            .n = n,
+        };
+        moe_cuda_bf16_to_f16(q->c, dev, pc);
+    }
+}
+
 /* mda_qwen_moe_mm, src/qwen.c:770-786 */
 static void moe_host_moe_mm(moe_host_t *q, void *a, uint32_t sa, void *w, void *out, void *tiles, uint32_t experts,
                             uint32_t m, uint32_t n, uint32_t k) {

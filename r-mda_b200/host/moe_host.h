@@ -51,6 +51,7 @@ bool moe_host_open(moe_host_t *q, moe_cuda_ctx_t *c, moe_host_cfg_t cfg, uint32_
 void moe_host_close(moe_host_t *q);
 void moe_host_slots_begin(moe_host_t *q);                        /* src/qwen.c:500-503 */
 uint32_t moe_host_slot(moe_host_t *q);                           /* src/qwen.c:505-515 */
+void moe_host_convert(moe_host_t *q, void *dev, uint64_t used_bytes);          /* mda_qwen_convert, src/qwen.c:365-378 */
 void moe_host_route_rec(moe_host_t *q, uint32_t rows, uint32_t mrows); /* src/qwen.c:788-836 */
 /* src/qwen.c:838-907 from the routing on; p and a16 must hold the upstream
  * projection and the fp16 activations.  h: fp32 [rows x hc x d], accumulated. */

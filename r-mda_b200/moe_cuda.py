@@ -46,6 +46,10 @@ class PcSlot(C.Structure):  # mda_pc_absmax_t and mda_pc_cast_t share this layou
     _fields_ = [("n", C.c_uint32), ("slot", C.c_uint32)]
 
 
+class PcBf16(C.Structure):
+    _fields_ = [("n", C.c_uint32)]
+
+
 class Layer(C.Structure):
     _fields_ = (
         [(n, C.c_uint32) for n in ("rows", "d", "experts", "topk", "inter", "shared", "pstride", "hc",
@@ -108,6 +112,7 @@ def lib() -> C.CDLL:
         L.moe_cuda_swiglu.argtypes = [vp, vp, vp, PcElem]
         L.moe_cuda_absmax.argtypes = [vp, vp, vp, PcSlot]
         L.moe_cuda_cast_f16.argtypes = [vp, vp, vp, vp, PcSlot]
+        L.moe_cuda_bf16_to_f16.argtypes = [vp, vp, PcBf16]
         L.moe_cuda_moe_rows.restype = u32
         L.moe_cuda_moe_rows.argtypes = [u32, u32, u32]
         L.moe_cuda_layer.argtypes = [vp, C.POINTER(Layer)]
@@ -258,6 +263,9 @@ class Ctx:
 
     def cast_f16(self, src, dst, amax, n, slot):
         lib().moe_cuda_cast_f16(self.p, _ptr(src), _ptr(dst), _ptr(amax), PcSlot(n, slot))
+
+    def bf16_to_f16(self, w, n_words):
+        lib().moe_cuda_bf16_to_f16(self.p, _ptr(w), PcBf16(n_words))
 
     def layer(self, **kw):
         L = Layer()

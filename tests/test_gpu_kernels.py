@@ -208,6 +208,19 @@ def test_glue(ctx, oracle, mc):
     assert 16384 <= np.abs(ref16.view(np.float16).astype(np.float32)).max() < 32768  # shader/cast_f16.comp scale
 
 
+def test_bf16_to_f16_in_place(ctx, oracle):
+    """The weight-upload conversion (shader/qwen_bf16.comp): bit-exact, odd word counts, specials."""
+    rng = np.random.default_rng(8)
+    for n_words in (1, 3, 4, 1000003):
+        bf = rng.integers(0, 1 << 16, 2 * n_words).astype(np.uint16)
+        bf[(bf & 0x7f80) == 0x7f80] &= 0xff80                            # keep infinities, drop NaN payloads
+        words = np.ascontiguousarray(bf.view(np.uint32))
+        d = ctx.upload(words)
+        ctx.bf16_to_f16(d, n_words)
+        ctx.flush()
+        assert np.array_equal(d.read(np.uint32, (n_words,)), oracle.bf16_to_f16(words))
+
+
 def test_fill_and_copy(ctx):
     b = ctx.alloc(4 * 1003)
     b.fill(0x12345678)

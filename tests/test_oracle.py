@@ -196,6 +196,19 @@ def test_residual_rmsnorm(oracle):
     assert np.allclose(y, want, rtol=2e-3, atol=1e-3)
 
 
+def test_bf16_to_f16(oracle):
+    rng = np.random.default_rng(6)
+    f = (rng.standard_normal(4096) * 10.0 ** rng.integers(-9, 6, 4096)).astype(np.float32)
+    bf = (f.view(np.uint32) >> 16).astype(np.uint16)                      # truncated bf16 bit patterns
+    bf[:6] = [0x0000, 0x8000, 0x7f80, 0xff80, 0x477f, 0x0001]            # +-0, +-inf, 65280, a bf16 denormal
+    words = np.ascontiguousarray(bf.view(np.uint32))
+    got = oracle.bf16_to_f16(words).view(np.uint16)
+    want = (bf.astype(np.uint32) << 16).view(np.float32)
+    with np.errstate(over="ignore"):
+        want16 = want.astype(np.float16).view(np.uint16)                  # numpy rounds to nearest even, overflow -> inf
+    assert np.array_equal(got, want16)
+
+
 def test_golden_vectors(oracle, synth):
     """The committed vectors were produced by tests/golden/make_golden.py from this oracle after
     it agreed with the numpy restatement; they catch any later drift of either."""
