@@ -1,7 +1,7 @@
 """Expert-parallel leg of bench.py (N > 1 GPUs of one box, one rank per GPU).
 
 Weak scaling: every rank brings T=4096 tokens of its own (global batch 4096*N) and owns E/N experts;
-dispatch and return cross NVLink inside the scatter and combine kernels."""
+a token row is dispatched once per destination GPU, expert output rows return inside the combine."""
 from __future__ import annotations
 
 import dataclasses
@@ -95,10 +95,14 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
     clocks = sampler.stop()
 
     idx = d_idx.read(np.uint32, (T, K))
-    remote_pairs = int((idx // el != rank).sum())
-    rp = torch.tensor([remote_pairs], device="cuda", dtype=torch.float64)
+    owner = idx // el
+    remote_pairs = int((owner != rank).sum())
+    dests = np.zeros((T, world), bool)
+    dests[np.arange(T)[:, None], owner] = True          # a row goes once to every GPU owning one of its experts
+    dests[:, rank] = False
+    rp = torch.tensor([remote_pairs, int(dests.sum())], device="cuda", dtype=torch.float64)
     dist.all_reduce(rp, op=dist.ReduceOp.MAX)
-    remote_pairs = int(rp.item())
+    remote_pairs, remote_rows = int(rp[0].item()), int(rp[1].item())
     ctx.flush()
 
     if rank == 0:
@@ -107,7 +111,8 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
         gemm1_flops = T * K * 4 * d * I   # per rank: on average every rank receives T*K rows
         tf1 = gemm1_flops / (stage_ms["gate_up"] * 1e-3) / 1e12
         tf2 = (gemm1_flops / 2) / (stage_ms["down"] * 1e-3) / 1e12
-        disp_bytes = remote_pairs * d * 2
+        disp_bytes = remote_rows * d * 2 + remote_pairs * 4   # rows once per GPU + one 4-byte record per pair
+        ret_bytes = remote_pairs * d * 2
         gbs = lambda b, m: b / (m * 1e-3) / 1e9 if m > 0 else None
         out = {
             "metric": METRIC, "value": T * world / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
@@ -121,12 +126,12 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
                          "achieved": tf1, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": tf1 / pk["bf16_tflops"],
                          "traffic": None, "peak_source": pk["source"] + " (burst)",
                          "flops_per_launch": gemm1_flops, "ms_per_launch": stage_ms["gate_up"]},
-            "nvlink": {"dispatch_bytes_per_gpu": disp_bytes, "return_bytes_per_gpu": disp_bytes,
-                       "dispatch_GB/s": gbs(disp_bytes, stage_ms["scatter"]), "return_GB/s": gbs(disp_bytes, stage_ms["combine"]),
+            "nvlink": {"dispatch_bytes_per_gpu": disp_bytes, "return_bytes_per_gpu": ret_bytes,
+                       "dispatch_GB/s": gbs(disp_bytes, stage_ms["scatter"]), "return_GB/s": gbs(ret_bytes, stage_ms["combine"]),
                        "peak_GB/s": nv_peak,
                        "dispatch_frac": gbs(disp_bytes, stage_ms["scatter"]) / nv_peak,
-                       "return_frac": gbs(disp_bytes, stage_ms["combine"]) / nv_peak,
-                       "note": "scatter stage = histogram + peer-store kernel + barrier; combine stage = peer-load gather"},
+                       "return_frac": gbs(ret_bytes, stage_ms["combine"]) / nv_peak,
+                       "note": "scatter stage = row send (once per destination GPU) + record scatter + barrier; combine stage = peer-load gather"},
             "stages_rank0_ms": {"route": stage_ms["route"], "counts all-gather + plan": stage_ms["scan"],
                                 "scatter + dispatch + barrier": stage_ms["scatter"], "gate_up": stage_ms["gate_up"],
                                 "down": stage_ms["down"], "barrier": stage_ms["shared"],

@@ -106,7 +106,8 @@ void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count,
                                uint32_t *off = NULL, uint32_t *tiles = NULL, uint32_t tile = 0);
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
-                      void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row = NULL);
+                      void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row = NULL,
+                      uint32_t *const *src_row_peers = NULL, uint32_t src_base = 0);
 
 enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // Grouped product.  mode F32: C fp32 [m x n] = A*B^T * s;  SWIGLU_F16: B holds

@@ -6,8 +6,12 @@
 //
 // The two all-to-alls are fused into the kernels on either side of them instead
 // of being library calls:
-//   dispatch: the scatter kernel writes each permuted row straight into the
-//             owning GPU's expert-contiguous buffer (peer stores over NVLink);
+//   dispatch: a token row crosses NVLink once per destination GPU, however many
+//             of its experts live there: the send kernel stores it into that
+//             GPU's receive buffer (slot = source rank, token), and the scatter
+//             kernel stores, for every (token, expert) pair, only a 4-byte record
+//             into the owner's source-row table; the owner's gate_up product
+//             gathers its operand rows through that table;
 //   return:   the combine kernel gathers each expert output row straight from
 //             the owning GPU's buffer (peer loads over NVLink).
 // Peer buffers are plain cudaMalloc memory mapped with CUDA IPC; all accesses
@@ -17,6 +21,9 @@
 // all ranks must have caught up -- counts complete, all rows landed, all products
 // done -- are flag barriers over peer memory with bounded waits.  NCCL is used
 // once, at set-up, to exchange the IPC handles.
+//
+// With top-8 routing over 8 GPUs a token has 7 remote expert copies but only 4.6
+// distinct remote GPUs on average; over 2 GPUs 4 copies but 1 GPU.
 //
 // Row order inside an expert is (source rank, token index); with contiguous
 // token blocks per rank that is the global token order, so the permutation is
@@ -79,11 +86,14 @@ struct moe_ep_state {
     uint32_t el;          // experts per rank
     uint32_t nmb;         // micro-batches: the local tokens are cut in nmb parts that pipeline transfer against products
     uint32_t mcap;        // rows of the expert-contiguous buffers of ONE micro-batch
-    __half *xp, *ye, *hp16;              // local [nmb * mcap x d], [nmb * mcap x d], [nmb * mcap x inter]
-    void *xp_peer[MOE_EP_MAX_WORLD];     // every rank's xp as mapped here (own entry = local pointer)
+    uint32_t cap;         // token rows one rank may send per micro-batch
+    __half *xr, *ye, *hp16;              // local [nmb * world * cap x d] received rows, [nmb * mcap x d], [nmb * mcap x inter]
+    void *xr_peer[MOE_EP_MAX_WORLD];     // every rank's xr as mapped here (own entry = local pointer)
     void *ye_peer[MOE_EP_MAX_WORLD];
-    void **xp_peer_dev[EP_MAX_MB], **ye_peer_dev[EP_MAX_MB];  // per micro-batch: each rank's buffer of that micro-batch
-    uint32_t *sync;                      // peer-visible: 6 x 16 epoch flags, then nmb tables [world][experts] of counts
+    void **xr_peer_dev[EP_MAX_MB], **ye_peer_dev[EP_MAX_MB];  // per micro-batch: each rank's buffer of that micro-batch
+    void **srow_peer_dev[EP_MAX_MB];     // per micro-batch: each rank's source-row table (inside its sync buffer)
+    uint32_t *src_row[EP_MAX_MB];        // own tables: expert-contiguous row -> row of xr (~0: padding)
+    uint32_t *sync;                      // peer-visible: 6 x 16 epoch flags, nmb tables [world][experts] of counts, nmb source-row tables [mcap]
     void *sync_peer[MOE_EP_MAX_WORLD];
     void **sync_peer_dev;
     uint32_t epoch;
@@ -129,12 +139,12 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
     if (c->stream != NULL) cudaStreamSynchronize(c->stream);
     for (int r = 0; r < ep->world; r += 1) {
         if (r == ep->rank) continue;
-        if (ep->xp_peer[r] != NULL) cudaIpcCloseMemHandle(ep->xp_peer[r]);
+        if (ep->xr_peer[r] != NULL) cudaIpcCloseMemHandle(ep->xr_peer[r]);
         if (ep->ye_peer[r] != NULL) cudaIpcCloseMemHandle(ep->ye_peer[r]);
         if (ep->sync_peer[r] != NULL) cudaIpcCloseMemHandle(ep->sync_peer[r]);
     }
-    void *mine[] = {ep->xp, ep->ye, ep->hp16, ep->xp_peer_dev[0], ep->ye_peer_dev[0], ep->xp_peer_dev[1], ep->ye_peer_dev[1],
-                    ep->sync_peer_dev, ep->sync, ep->dst_off[0], ep->dst_off[1], ep->tiles[0], ep->tiles[1], ep->count[0],
+    void *mine[] = {ep->xr, ep->ye, ep->hp16, ep->xr_peer_dev[0], ep->ye_peer_dev[0], ep->xr_peer_dev[1], ep->ye_peer_dev[1],
+                    ep->srow_peer_dev[0], ep->srow_peer_dev[1], ep->sync_peer_dev, ep->sync, ep->dst_off[0], ep->dst_off[1], ep->tiles[0], ep->tiles[1], ep->count[0],
                     ep->count[1], ep->idx, ep->slot, ep->bar, ep->wt};
     if (ep->side != NULL) {
         cudaStreamSynchronize(ep->side);
@@ -159,6 +169,9 @@ __global__ void moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t worl
 __global__ void moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch, uint32_t site,
                                    uint32_t table_off, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
                                    uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status);
+
+__global__ void moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xr_peers,
+                                   uint32_t rows, uint32_t topk, uint32_t d8, uint32_t el, uint32_t world, uint32_t src_base);
 
 // Joins the communicator, allocates the peer-visible buffers for the stated
 // maximum shape and maps every peer's buffers.  Collective over all ranks.
@@ -195,20 +208,23 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     ep->cfg = *cfg;
     ep->el = cfg->experts / (uint32_t)world;
     ep->mcap = mcap;
+    ep->cap = rows_mb;
     ep->nmb = nmb;
     ncclUniqueId id;
     memcpy(&id, unique_id128, sizeof(id));
     MOE_NCCL_TRY(c, g_nccl.CommInitRank(&ep->comm, world, id, rank));
 
     size_t R = cfg->max_rows, K = cfg->topk, E = cfg->experts;
-    const size_t sync_words = EP_FLAG_WORDS + (size_t)nmb * world * E;
-    ep->xp = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->d * 2);
+    const size_t srow_words0 = EP_FLAG_WORDS + (size_t)nmb * world * E;
+    const size_t sync_words = srow_words0 + (size_t)nmb * mcap;
+    ep->xr = (__half *)moe_cuda_alloc(c, (size_t)nmb * world * rows_mb * cfg->d * 2);
     ep->ye = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->d * 2);
     ep->hp16 = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->inter * 2);
     ep->sync = (uint32_t *)moe_cuda_alloc(c, sync_words * 4);
     ep->sync_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
     for (uint32_t m = 0; m < nmb; m += 1) {
-        ep->xp_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+        ep->xr_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+        ep->srow_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
         ep->ye_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
         ep->dst_off[m] = (uint32_t *)moe_cuda_alloc(c, E * 4);
         ep->tiles[m] = (uint32_t *)moe_cuda_alloc(c, (size_t)(mcap / MOE_TILE) * 4);
@@ -223,6 +239,7 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
         // the transfer kernels of one slice must be able to run on SMs that hold a product CTA of the other
         moe_overlap_prepare_combine(c);
         moe_overlap_prepare_scatter(c);
+        MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_send_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_barrier_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_plan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         if (c->status != MOE_OK) return;
@@ -234,12 +251,12 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->bar, 0, 256, c->stream));
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->sync, 0, sync_words * 4, c->stream));
 
-    // Exchange the IPC handles of xp and ye through the communicator itself.
+    // Exchange the IPC handles of xr, ye and sync through the communicator itself.
     struct Handles {
-        cudaIpcMemHandle_t xp, ye, sync;
+        cudaIpcMemHandle_t xr, ye, sync;
     };
     Handles mine;
-    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.xp, ep->xp));
+    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.xr, ep->xr));
     MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.ye, ep->ye));
     MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.sync, ep->sync));
     Handles *d_all = (Handles *)moe_cuda_alloc(c, sizeof(Handles) * (size_t)world);
@@ -252,23 +269,26 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     cudaFree(d_all);
     for (int r = 0; r < world; r += 1) {
         if (r == rank) {
-            ep->xp_peer[r] = ep->xp;
+            ep->xr_peer[r] = ep->xr;
             ep->ye_peer[r] = ep->ye;
             ep->sync_peer[r] = ep->sync;
             continue;
         }
-        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->xp_peer[r], all[r].xp, cudaIpcMemLazyEnablePeerAccess));
+        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->xr_peer[r], all[r].xr, cudaIpcMemLazyEnablePeerAccess));
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->ye_peer[r], all[r].ye, cudaIpcMemLazyEnablePeerAccess));
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->sync_peer[r], all[r].sync, cudaIpcMemLazyEnablePeerAccess));
     }
-    for (uint32_t m = 0; m < nmb; m += 1) {  // micro-batch m lives at row m * mcap of every rank's buffers
-        void *xt[MOE_EP_MAX_WORLD] = {}, *yt[MOE_EP_MAX_WORLD] = {};
+    for (uint32_t m = 0; m < nmb; m += 1) {  // micro-batch m: row m * mcap of ye, row m * world * cap of xr, table m
+        void *xt[MOE_EP_MAX_WORLD] = {}, *yt[MOE_EP_MAX_WORLD] = {}, *st[MOE_EP_MAX_WORLD] = {};
         for (int r = 0; r < world; r += 1) {
-            xt[r] = (__half *)ep->xp_peer[r] + (size_t)m * mcap * cfg->d;
+            xt[r] = (__half *)ep->xr_peer[r] + (size_t)m * world * rows_mb * cfg->d;
             yt[r] = (__half *)ep->ye_peer[r] + (size_t)m * mcap * cfg->d;
+            st[r] = (uint32_t *)ep->sync_peer[r] + srow_words0 + (size_t)m * mcap;
         }
-        MOE_CUDA_TRY(c, cudaMemcpy(ep->xp_peer_dev[m], xt, sizeof(xt), cudaMemcpyHostToDevice));
+        ep->src_row[m] = ep->sync + srow_words0 + (size_t)m * mcap;
+        MOE_CUDA_TRY(c, cudaMemcpy(ep->xr_peer_dev[m], xt, sizeof(xt), cudaMemcpyHostToDevice));
         MOE_CUDA_TRY(c, cudaMemcpy(ep->ye_peer_dev[m], yt, sizeof(yt), cudaMemcpyHostToDevice));
+        MOE_CUDA_TRY(c, cudaMemcpy(ep->srow_peer_dev[m], st, sizeof(st), cudaMemcpyHostToDevice));
     }
     MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->sync_peer_dev, ep->sync_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
     // nobody may write into a peer before every rank has finished mapping
@@ -367,6 +387,41 @@ moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_
     }
 }
 
+// Dispatch, bulk part: one warp per token reads the row once and stores it into the receive
+// buffer of every GPU that owns at least one of the token's experts (its own included: the
+// product gathers all its operand rows from the receive buffer), at row src_base + token.
+__global__ void __launch_bounds__(256)
+moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xr_peers,
+                   uint32_t rows, uint32_t topk, uint32_t d8, uint32_t el, uint32_t world, uint32_t src_base) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t r = warp; r < rows; r += nwarps) {
+        uint32_t bit = 0;
+        if (lane < topk) {
+            const uint32_t g = idx[(size_t)r * topk + lane] / el;
+            if (g < world) bit = 1u << g;  // a row the router refused carries ~0 and goes nowhere
+        }
+        const uint32_t mask = __reduce_or_sync(0xffffffffu, bit);
+        const uint4 *src = x16 + (size_t)r * d8;
+        for (uint32_t c0 = 0; c0 < d8; c0 += 256u) {
+            uint4 v[8];
+#pragma unroll
+            for (uint32_t i = 0; i < 8; i += 1) {
+                const uint32_t ci = c0 + i * 32u + lane;
+                if (ci < d8) v[i] = __ldg(src + ci);
+            }
+            for (uint32_t mk = mask; mk != 0; mk &= mk - 1u) {
+                uint4 *dst = xr_peers[__ffs((int)mk) - 1] + (size_t)(src_base + r) * d8;
+#pragma unroll
+                for (uint32_t i = 0; i < 8; i += 1) {
+                    const uint32_t ci = c0 + i * 32u + lane;
+                    if (ci < d8) dst[ci] = v[i];
+                }
+            }
+        }
+    }
+}
+
 extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
     if (!MOE_LIVE(c)) return;
     moe_ep_state *ep = c->ep;
@@ -389,7 +444,11 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         if (c->prof && c->ev_made && c->status == MOE_OK) cudaEventRecord(c->ev[i], main_stream);
     };
     mark(0);
-    for (uint32_t m = 0; m < nmb; m += 1) moe_cuda_fill(c, ep->tiles[m], (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
+    for (uint32_t m = 0; m < nmb; m += 1) {
+        moe_cuda_fill(c, ep->tiles[m], (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
+        // padding rows of used tiles read as zero; peers write the live entries after the first barrier
+        moe_cuda_fill(c, ep->src_row[m], (size_t)mcap * 4, 0xffffffffu);
+    }
     uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)((R + 7u) / 8u + 1u) * E * 4);
     if (hist == NULL) return;
     if (R != 0) moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride);
@@ -422,19 +481,25 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             // stagger: this slice's rows go out once the first slice's are on their way, under its products
             cudaStreamWaitEvent(c->stream, ep->ev_disp, 0);
         }
-        // dispatch fused into the scatter: rows go straight into their owner's buffer
+        // dispatch: each row once per destination GPU, then the 4-byte records of every (token, expert) pair
         if (rows != 0) {
-            moe_launch_place(c, idx + (size_t)row0 * K, ep->dst_off[m], hist + (size_t)(row0 / 8u) * E,
-                             (const __half *)L->x16 + (size_t)row0 * d, ep->xp + (size_t)m * mcap * d,
-                             slot + (size_t)row0 * K, rows, K, d / 8u, E, ep->xp_peer_dev[m], ep->el);
+            const uint32_t src_base = (uint32_t)ep->rank * ep->cap;
+            moe_ep_send_kernel<<<(rows + 7u) / 8u, 256, 0, c->stream>>>(
+                idx + (size_t)row0 * K, (const uint4 *)((const __half *)L->x16 + (size_t)row0 * d),
+                (uint4 *const *)ep->xr_peer_dev[m], rows, K, d / 8u, ep->el, (uint32_t)ep->world, src_base);
+            c->launches += 1;
+            moe_launch_place(c, idx + (size_t)row0 * K, ep->dst_off[m], hist + (size_t)(row0 / 8u) * E, L->x16, NULL,
+                             slot + (size_t)row0 * K, rows, K, d / 8u, E, NULL, ep->el, NULL,
+                             (uint32_t *const *)ep->srow_peer_dev[m], src_base);
         }
         if (m == 0 && nmb > 1) cudaEventRecord(ep->ev_disp, c->stream);
         moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
                                                        (uint32_t)ep->rank, site + 1u, ep->epoch, c->dev_status_dev);  // all rows landed
         c->launches += 1;
         if (m == 0) mark(3);
-        moe_launch_mm(c, MOE_MM_SWIGLU_F16, ep->xp + (size_t)m * mcap * d, L->wgu, ep->hp16 + (size_t)m * mcap * I, NULL,
-                      ep->tiles[m], mcap, 2u * I, d, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);
+        moe_launch_mm(c, MOE_MM_SWIGLU_F16, ep->xr + (size_t)m * ep->world * ep->cap * d, L->wgu, ep->hp16 + (size_t)m * mcap * I,
+                      NULL, ep->tiles[m], mcap, 2u * I, d, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el,
+                      (uint32_t)ep->world * ep->cap, true, ep->src_row[m]);
         if (m == 0) mark(4);
         moe_launch_mm(c, MOE_MM_F16, ep->hp16 + (size_t)m * mcap * I, L->wdown, ep->ye + (size_t)m * mcap * d, NULL,
                       ep->tiles[m], mcap, d, I, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);

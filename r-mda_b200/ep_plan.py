@@ -43,3 +43,11 @@ def local_ranks(idx: np.ndarray) -> np.ndarray:
     rank = np.empty(len(flat), np.int64)
     rank[order] = np.arange(len(flat)) - first
     return rank.reshape(idx.shape)
+
+
+def dest_ranks(idx: np.ndarray, el: int, world: int) -> np.ndarray:
+    """bool [T, world]: the GPUs a token row is sent to -- once each, however many of the token's
+    experts live there (the addressing of `moe_ep_send_kernel`)."""
+    mask = np.zeros((idx.shape[0], world), bool)
+    mask[np.arange(idx.shape[0])[:, None], idx // el] = True
+    return mask

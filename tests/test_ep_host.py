@@ -55,15 +55,29 @@ def _worker(rank, world, port, T_local, fail_rank, q):
         want_row = (full.slot[lo:hi].astype(np.int64) - full.off[idx].astype(np.int64)
                     + np.array([epp.plan(cnt_all, o)[1] for o in range(world)]).reshape(-1)[idx])
         assert np.array_equal(dest_row, want_row)
-        # "peer stores": every rank learns all (owner, row, data) triples and keeps its own
+        # dispatch: a row travels once per destination rank into that rank's receive buffer (slot =
+        # source rank, token); every (token, expert) pair travels as a 4-byte record into the owner's
+        # source-row table.  Every rank learns all of it and keeps what is addressed to it.
         mcap = epp.ep_rows(world, T_local, cfg.E, cfg.K)
+        dests = epp.dest_ranks(idx, el, world)
+        assert dests.sum() <= owner.size and np.array_equal(dests.any(1), np.ones(T_local, bool))
         objs = [None] * world
-        dist.all_gather_object(objs, (owner.ravel(), dest_row.ravel(), np.repeat(x16, cfg.K, 0)))
-        xp = np.zeros((mcap, cfg.d), np.uint16)
-        for ow, rows, data in objs:
-            sel = ow == rank
-            assert not xp[rows[sel]].any()          # no two pairs land on the same row
-            xp[rows[sel]] = data[sel]
+        dist.all_gather_object(objs, (rank, dests, x16, owner.ravel(), dest_row.ravel(),
+                                      np.repeat(np.arange(T_local), cfg.K)))
+        xr = np.full((world * T_local, cfg.d), 0x7e00, np.uint16)      # fp16 NaN: a row that never arrived would show
+        have = np.zeros(world * T_local, bool)
+        src_row = np.full(mcap, -1, np.int64)
+        for s, dst, rows_x, ow, drow, tok in objs:
+            sel = dst[:, rank]
+            xr[s * T_local + np.nonzero(sel)[0]] = rows_x[sel]
+            have[s * T_local + np.nonzero(sel)[0]] = True
+            selp = ow == rank
+            assert (src_row[drow[selp]] == -1).all()      # no two pairs land on the same row
+            src_row[drow[selp]] = s * T_local + tok[selp]
+        live = src_row >= 0
+        assert have[src_row[live]].all()                  # every row a record points at was sent
+        xp = np.zeros((mcap, cfg.d), np.uint16)           # what the owner's product gathers
+        xp[live] = xr[src_row[live]]
         tl = np.full(mcap // 128, 0xffffffff, np.uint32)
         tl[:len(tiles)] = tiles
         g = O.mm(xp, wgu, tl, 2 * cfg.I, cfg.d)
