@@ -198,9 +198,12 @@ void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
  *      reference, which keeps all experts of a layer on one device,
  *      src/qwen.c:235-246) ------------------------------------------------
  * One process per GPU.  Rank g owns experts [g*E/G, (g+1)*E/G) and passes only
- * their weights; every rank passes its own tokens.  Dispatch and return are
- * fused into the scatter and combine kernels as peer stores / loads over
- * NVLink; the per-expert counts and the three rendezvous points per layer are
+ * their weights; every rank passes its own tokens.  Dispatch: each token row
+ * is stored once into the receive buffer of every GPU that owns one of its
+ * experts, plus one 4-byte record per (token, expert) pair into the owner's
+ * source-row table, through which the owner's gate_up product gathers its
+ * operand; return: the combine kernel loads each expert-output row from its
+ * owner.  All of it is plain peer stores / loads over NVLink; the per-expert counts and the three rendezvous points per layer are
  * flag exchanges over the same peer memory with bounded waits (a rank that
  * stops coming ends the others' call with MOE_ERR_TIMEOUT after 2 s).  NCCL is
  * needed once, at moe_cuda_ep_init, to hand round the memory handles. */
