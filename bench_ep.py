@@ -1,7 +1,7 @@
 """Expert-parallel leg of bench.py (N > 1 GPUs of one box, one rank per GPU).
 
 Weak scaling: every rank brings T=4096 tokens of its own (global batch 4096*N) and owns E/N experts;
-a token row is dispatched once per destination GPU, expert output rows return inside the combine."""
+a token row is dispatched once per destination GPU and one partial output row returns per owning GPU."""
 from __future__ import annotations
 
 import dataclasses
@@ -112,7 +112,7 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
         tf1 = gemm1_flops / (stage_ms["gate_up"] * 1e-3) / 1e12
         tf2 = (gemm1_flops / 2) / (stage_ms["down"] * 1e-3) / 1e12
         disp_bytes = remote_rows * d * 2 + remote_pairs * 4   # rows once per GPU + one 4-byte record per pair
-        ret_bytes = remote_pairs * d * 2
+        ret_bytes = remote_rows * d * 2                       # one fp16 partial row per (token, owning GPU)
         gbs = lambda b, m: b / (m * 1e-3) / 1e9 if m > 0 else None
         out = {
             "metric": METRIC, "value": T * world / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
@@ -131,7 +131,7 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
                        "peak_GB/s": nv_peak,
                        "dispatch_frac": gbs(disp_bytes, stage_ms["scatter"]) / nv_peak,
                        "return_frac": gbs(ret_bytes, stage_ms["combine"]) / nv_peak,
-                       "note": "scatter stage = row send (once per destination GPU) + record scatter + barrier; combine stage = peer-load gather"},
+                       "note": "scatter stage = row send (once per destination GPU) + record scatter + barrier; combine stage = peer loads of one partial row per owning GPU (the owner-side partial sums sit in the down stage)"},
             "stages_rank0_ms": {"route": stage_ms["route"], "counts all-gather + plan": stage_ms["scan"],
                                 "scatter + dispatch + barrier": stage_ms["scatter"], "gate_up": stage_ms["gate_up"],
                                 "down": stage_ms["down"], "barrier": stage_ms["shared"],

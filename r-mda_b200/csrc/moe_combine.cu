@@ -29,12 +29,30 @@ moe_combine_kernel(moe_combine_args a) {
     __shared__ float s_f[8];
     __shared__ float s_red[CB_THREADS / 32];
     __shared__ const YT *s_y[PEER ? MOE_MAX_TOPK : 1];
+    __shared__ uint32_t s_mask, s_terms;
     uint32_t r = blockIdx.x;
     const YT *y = reinterpret_cast<const YT *>(a.y);
-    if (threadIdx.x < a.topk) {
-        if (PEER) {  // expert-parallel: the row is read from the GPU that owns its expert, over NVLink
-            s_y[threadIdx.x] = reinterpret_cast<const YT *>(a.y_peers[a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank]);
+    if (PEER) {
+        // Expert-parallel: every GPU that owns some of the token's experts has already summed
+        // wt * row over those experts (moe_ep_partial_kernel); one such partial row per GPU comes
+        // over NVLink and the partial rows are added in ascending GPU order.
+        if (threadIdx.x == 0) s_mask = 0;
+        __syncthreads();
+        if (threadIdx.x < a.topk) {
+            uint32_t g = a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank;
+            if (g < MOE_MAX_TOPK) atomicOr(&s_mask, 1u << g);
         }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t n = 0;
+            for (uint32_t mk = s_mask; mk != 0; mk &= mk - 1u, n += 1) {
+                s_y[n] = reinterpret_cast<const YT *>(a.y_peers[__ffs((int)mk) - 1]);
+                s_slot[n] = a.src_base + r;
+                s_wt[n] = 1.0f;
+            }
+            s_terms = n;
+        }
+    } else if (threadIdx.x < a.topk) {
         s_slot[threadIdx.x] = a.slot[(size_t)r * a.topk + threadIdx.x];
         s_wt[threadIdx.x] = a.wt[(size_t)r * a.topk + threadIdx.x];
     }
@@ -47,13 +65,14 @@ moe_combine_kernel(moe_combine_args a) {
         s_f[7] = a.sh != NULL ? moe_sigmoid(a.proj[(size_t)r * a.pstride + a.sg_off]) : 0.0f;  // :35
     }
     __syncthreads();
+    const uint32_t terms = PEER ? s_terms : a.topk;
     float sg = s_f[7];
     float4 keep[NORM ? CB_MAXV : 1];
     float ss = 0.0f;
     uint32_t it = 0;
     for (uint32_t c = threadIdx.x * 4u; c < a.d; c += CB_THREADS * 4u, it += 1) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t j = 0; j < a.topk; j += 1) {
+        for (uint32_t j = 0; j < terms; j += 1) {
             float4 v = moe_load4((PEER ? s_y[j] : y) + (size_t)s_slot[j] * a.d + c);
             float w = s_wt[j];
             acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
@@ -128,7 +147,7 @@ void moe_overlap_prepare_combine(moe_cuda_ctx *c) {
 
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a) {
     if (!MOE_LIVE(c)) return;
-    MOE_REQUIRE(c, a.wt != NULL && a.slot != NULL && (a.y != NULL || a.y_peers != NULL), "combine: null buffer");
+    MOE_REQUIRE(c, a.y_peers != NULL || (a.wt != NULL && a.slot != NULL && a.y != NULL), "combine: null buffer");
     MOE_REQUIRE(c, a.y_peers == NULL || (a.idx != NULL && a.experts_per_rank >= 1), "combine: peer rows need idx");
     MOE_REQUIRE(c, a.h != NULL || a.y16 != NULL, "combine: no output");
     MOE_REQUIRE(c, a.sh == NULL || a.proj != NULL, "combine: shared term needs proj");

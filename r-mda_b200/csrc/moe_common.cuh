@@ -107,7 +107,8 @@ void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count,
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
                       void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row = NULL,
-                      uint32_t *const *src_row_peers = NULL, uint32_t src_base = 0);
+                      uint32_t *const *src_row_peers = NULL, uint32_t src_base = 0, uint2 *const *ret_peers = NULL,
+                      const float *wt = NULL);
 
 enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // Grouped product.  mode F32: C fp32 [m x n] = A*B^T * s;  SWIGLU_F16: B holds
@@ -140,10 +141,12 @@ struct moe_combine_args {
     float eps;
     uint32_t rows, d, topk, pstride, sg_off, inj_stride, inj_off, hc;
     bool y_is_f16;
-    // expert-parallel: row j of a token lives in y_peers[idx[r,j] / experts_per_rank]
+    // expert-parallel: GPU g = idx[r,j] / experts_per_rank holds, in y_peers[g] at row src_base + r,
+    // the token's weighted sum over its experts there (fp16); wt, slot and y are then unused
     const uint32_t *idx;
     const void *const *y_peers;
     uint32_t experts_per_rank;
+    uint32_t src_base;
 };
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a);
 void moe_overlap_prepare_combine(moe_cuda_ctx *c);

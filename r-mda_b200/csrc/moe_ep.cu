@@ -12,8 +12,12 @@
 //             kernel stores, for every (token, expert) pair, only a 4-byte record
 //             into the owner's source-row table; the owner's gate_up product
 //             gathers its operand rows through that table;
-//   return:   the combine kernel gathers each expert output row straight from
-//             the owning GPU's buffer (peer loads over NVLink).
+//   return:   the same the other way round: the owner sums wt * (expert output
+//             row) over the token's experts it holds (moe_ep_partial_kernel, from
+//             8-byte records the scatter kernel stored beside the source-row
+//             records) and the home GPU's combine kernel loads that one fp16
+//             partial row per owning GPU (peer loads over NVLink), adding the
+//             partial rows in ascending GPU order.
 // Peer buffers are plain cudaMalloc memory mapped with CUDA IPC; all accesses
 // are ordinary ld/st (no multimem, no TMA from peer memory: the grouped
 // products only ever read local HBM).  The per-expert counts travel the same way
@@ -87,13 +91,15 @@ struct moe_ep_state {
     uint32_t nmb;         // micro-batches: the local tokens are cut in nmb parts that pipeline transfer against products
     uint32_t mcap;        // rows of the expert-contiguous buffers of ONE micro-batch
     uint32_t cap;         // token rows one rank may send per micro-batch
-    __half *xr, *ye, *hp16;              // local [nmb * world * cap x d] received rows, [nmb * mcap x d], [nmb * mcap x inter]
+    __half *xr, *part, *ye, *hp16;       // [nmb * world * cap x d] received rows, the same shape of partial output rows; local only: [nmb * mcap x d], [nmb * mcap x inter]
     void *xr_peer[MOE_EP_MAX_WORLD];     // every rank's xr as mapped here (own entry = local pointer)
-    void *ye_peer[MOE_EP_MAX_WORLD];
-    void **xr_peer_dev[EP_MAX_MB], **ye_peer_dev[EP_MAX_MB];  // per micro-batch: each rank's buffer of that micro-batch
+    void *part_peer[MOE_EP_MAX_WORLD];
+    void **xr_peer_dev[EP_MAX_MB], **part_peer_dev[EP_MAX_MB];  // per micro-batch: each rank's buffer of that micro-batch
     void **srow_peer_dev[EP_MAX_MB];     // per micro-batch: each rank's source-row table (inside its sync buffer)
+    void **ret_peer_dev[EP_MAX_MB];      // per micro-batch: each rank's return-record table (inside its sync buffer)
     uint32_t *src_row[EP_MAX_MB];        // own tables: expert-contiguous row -> row of xr (~0: padding)
-    uint32_t *sync;                      // peer-visible: 6 x 16 epoch flags, nmb tables [world][experts] of counts, nmb source-row tables [mcap]
+    uint2 *ret_tab[EP_MAX_MB];           // own tables: [world * cap][topk] (output row, weight) per received token, ~0 ends a list
+    uint32_t *sync;                      // peer-visible: 6 x 16 epoch flags, nmb tables [world][experts] of counts, nmb source-row tables [mcap], nmb return tables
     void *sync_peer[MOE_EP_MAX_WORLD];
     void **sync_peer_dev;
     uint32_t epoch;
@@ -140,11 +146,11 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
     for (int r = 0; r < ep->world; r += 1) {
         if (r == ep->rank) continue;
         if (ep->xr_peer[r] != NULL) cudaIpcCloseMemHandle(ep->xr_peer[r]);
-        if (ep->ye_peer[r] != NULL) cudaIpcCloseMemHandle(ep->ye_peer[r]);
+        if (ep->part_peer[r] != NULL) cudaIpcCloseMemHandle(ep->part_peer[r]);
         if (ep->sync_peer[r] != NULL) cudaIpcCloseMemHandle(ep->sync_peer[r]);
     }
-    void *mine[] = {ep->xr, ep->ye, ep->hp16, ep->xr_peer_dev[0], ep->ye_peer_dev[0], ep->xr_peer_dev[1], ep->ye_peer_dev[1],
-                    ep->srow_peer_dev[0], ep->srow_peer_dev[1], ep->sync_peer_dev, ep->sync, ep->dst_off[0], ep->dst_off[1], ep->tiles[0], ep->tiles[1], ep->count[0],
+    void *mine[] = {ep->xr, ep->part, ep->ye, ep->hp16, ep->xr_peer_dev[0], ep->part_peer_dev[0], ep->xr_peer_dev[1], ep->part_peer_dev[1],
+                    ep->srow_peer_dev[0], ep->srow_peer_dev[1], ep->ret_peer_dev[0], ep->ret_peer_dev[1], ep->sync_peer_dev, ep->sync, ep->dst_off[0], ep->dst_off[1], ep->tiles[0], ep->tiles[1], ep->count[0],
                     ep->count[1], ep->idx, ep->slot, ep->bar, ep->wt};
     if (ep->side != NULL) {
         cudaStreamSynchronize(ep->side);
@@ -172,6 +178,9 @@ __global__ void moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32
 
 __global__ void moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xr_peers,
                                    uint32_t rows, uint32_t topk, uint32_t d8, uint32_t el, uint32_t world, uint32_t src_base);
+
+__global__ void moe_ep_partial_kernel(const uint2 *__restrict__ ret_tab, const uint4 *__restrict__ ye, uint4 *__restrict__ part,
+                                      uint32_t slots, uint32_t topk, uint32_t d8);
 
 // Joins the communicator, allocates the peer-visible buffers for the stated
 // maximum shape and maps every peer's buffers.  Collective over all ranks.
@@ -216,8 +225,11 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
 
     size_t R = cfg->max_rows, K = cfg->topk, E = cfg->experts;
     const size_t srow_words0 = EP_FLAG_WORDS + (size_t)nmb * world * E;
-    const size_t sync_words = srow_words0 + (size_t)nmb * mcap;
+    const size_t ret_words0 = (srow_words0 + (size_t)nmb * mcap + 1u) & ~(size_t)1u;  // 8-byte records
+    const size_t ret_words = (size_t)world * rows_mb * K * 2u;                          // per micro-batch
+    const size_t sync_words = ret_words0 + (size_t)nmb * ret_words;
     ep->xr = (__half *)moe_cuda_alloc(c, (size_t)nmb * world * rows_mb * cfg->d * 2);
+    ep->part = (__half *)moe_cuda_alloc(c, (size_t)nmb * world * rows_mb * cfg->d * 2);
     ep->ye = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->d * 2);
     ep->hp16 = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->inter * 2);
     ep->sync = (uint32_t *)moe_cuda_alloc(c, sync_words * 4);
@@ -225,7 +237,8 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     for (uint32_t m = 0; m < nmb; m += 1) {
         ep->xr_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
         ep->srow_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
-        ep->ye_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+        ep->part_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+        ep->ret_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
         ep->dst_off[m] = (uint32_t *)moe_cuda_alloc(c, E * 4);
         ep->tiles[m] = (uint32_t *)moe_cuda_alloc(c, (size_t)(mcap / MOE_TILE) * 4);
         ep->count[m] = (uint32_t *)moe_cuda_alloc(c, E * 4);
@@ -240,6 +253,7 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
         moe_overlap_prepare_combine(c);
         moe_overlap_prepare_scatter(c);
         MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_send_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_partial_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_barrier_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_plan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         if (c->status != MOE_OK) return;
@@ -251,13 +265,13 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->bar, 0, 256, c->stream));
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->sync, 0, sync_words * 4, c->stream));
 
-    // Exchange the IPC handles of xr, ye and sync through the communicator itself.
+    // Exchange the IPC handles of xr, part and sync through the communicator itself.
     struct Handles {
-        cudaIpcMemHandle_t xr, ye, sync;
+        cudaIpcMemHandle_t xr, part, sync;
     };
     Handles mine;
     MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.xr, ep->xr));
-    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.ye, ep->ye));
+    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.part, ep->part));
     MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.sync, ep->sync));
     Handles *d_all = (Handles *)moe_cuda_alloc(c, sizeof(Handles) * (size_t)world);
     if (d_all == NULL) return;
@@ -270,25 +284,28 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     for (int r = 0; r < world; r += 1) {
         if (r == rank) {
             ep->xr_peer[r] = ep->xr;
-            ep->ye_peer[r] = ep->ye;
+            ep->part_peer[r] = ep->part;
             ep->sync_peer[r] = ep->sync;
             continue;
         }
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->xr_peer[r], all[r].xr, cudaIpcMemLazyEnablePeerAccess));
-        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->ye_peer[r], all[r].ye, cudaIpcMemLazyEnablePeerAccess));
+        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->part_peer[r], all[r].part, cudaIpcMemLazyEnablePeerAccess));
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->sync_peer[r], all[r].sync, cudaIpcMemLazyEnablePeerAccess));
     }
-    for (uint32_t m = 0; m < nmb; m += 1) {  // micro-batch m: row m * mcap of ye, row m * world * cap of xr, table m
-        void *xt[MOE_EP_MAX_WORLD] = {}, *yt[MOE_EP_MAX_WORLD] = {}, *st[MOE_EP_MAX_WORLD] = {};
+    for (uint32_t m = 0; m < nmb; m += 1) {  // micro-batch m: row m * world * cap of xr and part, tables m
+        void *xt[MOE_EP_MAX_WORLD] = {}, *yt[MOE_EP_MAX_WORLD] = {}, *st[MOE_EP_MAX_WORLD] = {}, *rt[MOE_EP_MAX_WORLD] = {};
         for (int r = 0; r < world; r += 1) {
             xt[r] = (__half *)ep->xr_peer[r] + (size_t)m * world * rows_mb * cfg->d;
-            yt[r] = (__half *)ep->ye_peer[r] + (size_t)m * mcap * cfg->d;
+            yt[r] = (__half *)ep->part_peer[r] + (size_t)m * world * rows_mb * cfg->d;
             st[r] = (uint32_t *)ep->sync_peer[r] + srow_words0 + (size_t)m * mcap;
+            rt[r] = (uint32_t *)ep->sync_peer[r] + ret_words0 + (size_t)m * ret_words;
         }
         ep->src_row[m] = ep->sync + srow_words0 + (size_t)m * mcap;
+        ep->ret_tab[m] = (uint2 *)(ep->sync + ret_words0 + (size_t)m * ret_words);
         MOE_CUDA_TRY(c, cudaMemcpy(ep->xr_peer_dev[m], xt, sizeof(xt), cudaMemcpyHostToDevice));
-        MOE_CUDA_TRY(c, cudaMemcpy(ep->ye_peer_dev[m], yt, sizeof(yt), cudaMemcpyHostToDevice));
+        MOE_CUDA_TRY(c, cudaMemcpy(ep->part_peer_dev[m], yt, sizeof(yt), cudaMemcpyHostToDevice));
         MOE_CUDA_TRY(c, cudaMemcpy(ep->srow_peer_dev[m], st, sizeof(st), cudaMemcpyHostToDevice));
+        MOE_CUDA_TRY(c, cudaMemcpy(ep->ret_peer_dev[m], rt, sizeof(rt), cudaMemcpyHostToDevice));
     }
     MOE_CUDA_TRY(c, cudaMemcpyAsync(ep->sync_peer_dev, ep->sync_peer, sizeof(void *) * MOE_EP_MAX_WORLD, cudaMemcpyHostToDevice, c->stream));
     // nobody may write into a peer before every rank has finished mapping
@@ -422,6 +439,74 @@ moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x
     }
 }
 
+// Return, owner side: a warp takes one received token slot and one 2 KB piece of its row, adds
+// wt * (expert output row) over the token's records in list order (fp32, multiply and add rounded
+// separately as in the combine) and leaves fp16; the next record's loads are issued before the
+// current one is accumulated.  A slot whose list is empty is skipped and never read by its home GPU.
+__global__ void __launch_bounds__(256)
+moe_ep_partial_kernel(const uint2 *__restrict__ ret_tab, const uint4 *__restrict__ ye, uint4 *__restrict__ part,
+                      uint32_t slots, uint32_t topk, uint32_t d8) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const uint32_t pieces = (d8 + 127u) / 128u;  // 128 x 16 bytes per piece: four 16-byte loads per lane
+    for (uint32_t u = warp; u < slots * pieces; u += nwarps) {
+        const uint32_t t = u / pieces, c0 = (u - t * pieces) * 128u;
+        const uint2 *rec = ret_tab + (size_t)t * topk;
+        const uint2 mine = lane < topk ? rec[lane] : make_uint2(~0u, 0u);
+        const uint32_t n = (uint32_t)__popc(__ballot_sync(0xffffffffu, mine.x != ~0u));  // lists are packed from entry 0
+        if (n == 0) continue;
+        float acc[4][8];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i += 1) {
+#pragma unroll
+            for (uint32_t q = 0; q < 8; q += 1) acc[i][q] = 0.0f;
+        }
+        uint4 cur[4], nxt[4];
+        {
+            const uint4 *src = ye + (size_t)__shfl_sync(0xffffffffu, mine.x, 0) * d8;
+#pragma unroll
+            for (uint32_t i = 0; i < 4; i += 1) {
+                const uint32_t ci = c0 + i * 32u + lane;
+                cur[i] = ci < d8 ? src[ci] : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        for (uint32_t j = 0; j < n; j += 1) {
+            const float w = __uint_as_float(__shfl_sync(0xffffffffu, mine.y, j));
+            if (j + 1u < n) {
+                const uint4 *src = ye + (size_t)__shfl_sync(0xffffffffu, mine.x, j + 1u) * d8;
+#pragma unroll
+                for (uint32_t i = 0; i < 4; i += 1) {
+                    const uint32_t ci = c0 + i * 32u + lane;
+                    nxt[i] = ci < d8 ? src[ci] : make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < 4; i += 1) {
+                const __half2 *h = reinterpret_cast<const __half2 *>(&cur[i]);
+#pragma unroll
+                for (uint32_t q = 0; q < 4; q += 1) {
+                    const float2 f = __half22float2(h[q]);
+                    acc[i][2 * q] = __fadd_rn(acc[i][2 * q], __fmul_rn(w, f.x));
+                    acc[i][2 * q + 1] = __fadd_rn(acc[i][2 * q + 1], __fmul_rn(w, f.y));
+                }
+                cur[i] = nxt[i];
+            }
+        }
+        uint4 *dst = part + (size_t)t * d8;
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i += 1) {
+            const uint32_t ci = c0 + i * 32u + lane;
+            if (ci < d8) {
+                uint4 o;
+                __half2 *h = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+                for (uint32_t q = 0; q < 4; q += 1) h[q] = __floats2half2_rn(acc[i][2 * q], acc[i][2 * q + 1]);
+                dst[ci] = o;
+            }
+        }
+    }
+}
+
 extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
     if (!MOE_LIVE(c)) return;
     moe_ep_state *ep = c->ep;
@@ -448,6 +533,8 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         moe_cuda_fill(c, ep->tiles[m], (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
         // padding rows of used tiles read as zero; peers write the live entries after the first barrier
         moe_cuda_fill(c, ep->src_row[m], (size_t)mcap * 4, 0xffffffffu);
+        // return records: ~0 ends a token's list
+        moe_cuda_fill(c, ep->ret_tab[m], (size_t)ep->world * ep->cap * K * 8, 0xffffffffu);
     }
     uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)((R + 7u) / 8u + 1u) * E * 4);
     if (hist == NULL) return;
@@ -490,7 +577,8 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             c->launches += 1;
             moe_launch_place(c, idx + (size_t)row0 * K, ep->dst_off[m], hist + (size_t)(row0 / 8u) * E, L->x16, NULL,
                              slot + (size_t)row0 * K, rows, K, d / 8u, E, NULL, ep->el, NULL,
-                             (uint32_t *const *)ep->srow_peer_dev[m], src_base);
+                             (uint32_t *const *)ep->srow_peer_dev[m], src_base, (uint2 *const *)ep->ret_peer_dev[m],
+                             wt + (size_t)row0 * K);
         }
         if (m == 0 && nmb > 1) cudaEventRecord(ep->ev_disp, c->stream);
         moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
@@ -503,9 +591,17 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         if (m == 0) mark(4);
         moe_launch_mm(c, MOE_MM_F16, ep->hp16 + (size_t)m * mcap * I, L->wdown, ep->ye + (size_t)m * mcap * d, NULL,
                       ep->tiles[m], mcap, d, I, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);
+        {   // return, owner side: one weighted partial row per received token
+            const uint32_t slots = (uint32_t)ep->world * ep->cap;
+            const uint32_t units = slots * ((d / 8u + 127u) / 128u);  // one warp per (slot, 2 KB piece)
+            moe_ep_partial_kernel<<<(units + 7u) / 8u, 256, 0, c->stream>>>(
+                ep->ret_tab[m], (const uint4 *)(ep->ye + (size_t)m * mcap * d),
+                (uint4 *)(ep->part + (size_t)m * ep->world * ep->cap * d), slots, K, d / 8u);
+            c->launches += 1;
+        }
         if (m == 0) mark(5);
         moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
-                                                       (uint32_t)ep->rank, site + 2u, ep->epoch, c->dev_status_dev);  // all products done
+                                                       (uint32_t)ep->rank, site + 2u, ep->epoch, c->dev_status_dev);  // all partial rows written
         c->launches += 1;
         if (m == 0) mark(6);
         if (rows != 0) {
@@ -529,9 +625,10 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             a.hc = L->hc;
             a.y_is_f16 = true;
             a.idx = idx + (size_t)row0 * K;
-            a.y_peers = (const void *const *)ep->ye_peer_dev[m];
+            a.y_peers = (const void *const *)ep->part_peer_dev[m];
             a.experts_per_rank = ep->el;
-            moe_launch_combine(c, a);  // return all-to-all fused into the gather
+            a.src_base = (uint32_t)ep->rank * ep->cap;
+            moe_launch_combine(c, a);  // return all-to-all fused into the gather: one partial row per owning GPU
         }
         if (m == 0) mark(7);
     }

@@ -112,7 +112,7 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
                          uint4 *__restrict__ xp, uint32_t *__restrict__ slot, uint32_t pairs, uint32_t topk,
                          uint32_t d8, uint32_t ebound, uint4 *const *__restrict__ xp_peers, uint32_t experts_per_rank,
                          uint32_t ppb, uint32_t *__restrict__ src_row, uint32_t *const *__restrict__ src_row_peers,
-                         uint32_t src_base) {
+                         uint32_t src_base, uint2 *const *__restrict__ ret_peers, const float *__restrict__ wt) {
     // ppb = pairs per block (<= SC_MAX_PAIRS): 64 in the stand-alone scatter, 8*topk behind the fused router
     __shared__ uint32_t s_e[SC_MAX_PAIRS];
     __shared__ uint32_t s_slot[SC_MAX_PAIRS];
@@ -135,7 +135,18 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
             if (src_row != NULL) src_row[p] = (p0 + threadIdx.x) / topk;
             // expert-parallel gather mode: the record goes into the owning GPU's table; the row itself
             // travels once per destination GPU (moe_ep_send_kernel) and sits at src_base + its local index
-            else if (src_row_peers != NULL) src_row_peers[e / experts_per_rank][p] = src_base + (p0 + threadIdx.x) / topk;
+            else if (src_row_peers != NULL) {
+                const uint32_t g = e / experts_per_rank, row = src_base + (p0 + threadIdx.x) / topk;
+                src_row_peers[g][p] = row;
+                if (ret_peers != NULL) {
+                    // return record: (row of the expert's output, router weight), the token's records on one
+                    // GPU packed in j order (ppb is a multiple of topk, so a token's pairs share the block)
+                    const uint32_t t0 = threadIdx.x - threadIdx.x % topk;
+                    uint32_t jj = 0;
+                    for (uint32_t q = t0; q < threadIdx.x; q += 1) jj += (s_e[q] < ebound && s_e[q] / experts_per_rank == g) ? 1u : 0u;
+                    ret_peers[g][(size_t)row * topk + jj] = make_uint2(p, __float_as_uint(wt[p0 + threadIdx.x]));
+                }
+            }
         } else {
             s_slot[threadIdx.x] = ~0u;
         }
@@ -182,7 +193,7 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp,
                                                                     slot, pairs, topk, d8, ebound,
-                                                                    (uint4 *const *)xp_peers, experts_per_rank, SC_PAIRS, NULL, NULL, 0);
+                                                                    (uint4 *const *)xp_peers, experts_per_rank, SC_PAIRS, NULL, NULL, 0, NULL, NULL);
     MOE_LAUNCHED(c);
 }
 
@@ -218,7 +229,7 @@ void moe_overlap_prepare_scatter(moe_cuda_ctx *c) {
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
                       void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row, uint32_t *const *src_row_peers,
-                      uint32_t src_base) {
+                      uint32_t src_base, uint2 *const *ret_peers, const float *wt) {
     if (!MOE_LIVE(c)) return;
     if (rows == 0) return;
     MOE_REQUIRE(c, ((uintptr_t)x16 & 15) == 0 && ((uintptr_t)xp & 15) == 0, "scatter: rows not 16-byte aligned");
@@ -226,7 +237,7 @@ void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off,
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp, slot,
                                                                     rows * topk, topk, d8, experts,
                                                                     (uint4 *const *)xp_peers, experts_per_rank, 8u * topk, src_row,
-                                                                    src_row_peers, src_base);
+                                                                    src_row_peers, src_base, ret_peers, wt);
     MOE_LAUNCHED(c);
 }
 
@@ -289,6 +300,6 @@ extern "C" void moe_cuda_scatter_noalloc(moe_cuda_ctx_t *c, const uint32_t *idx,
     moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts, NULL, NULL, NULL, NULL, 0);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<(uint32_t)nblocks, SC_THREADS, 0, c->stream>>>(
-        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0, SC_PAIRS, NULL, NULL, 0);
+        idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0, SC_PAIRS, NULL, NULL, 0, NULL, NULL);
     MOE_LAUNCHED(c);
 }

@@ -1,5 +1,6 @@
 """Expert-parallel host logic on CPU: two gloo ranks run the layout arithmetic of the EP path
-(counts exchange, destination rows, owner-side tile schedule, gather back) with the CPU oracle
+(counts exchange, rows sent once per destination rank, owner-side tile schedule and source-row table,
+partial sums per owning rank on the way back) with the CPU oracle
 standing in for the kernels, and must reproduce the single-process layer."""
 import os
 import socket
@@ -83,13 +84,21 @@ def _worker(rank, world, port, T_local, fail_rank, q):
         g = O.mm(xp, wgu, tl, 2 * cfg.I, cfg.d)
         hp16 = O.cast_f16(O.swiglu(g, cfg.I, 2 * cfg.I, 0, cfg.I), np.zeros(4, np.uint32), O.NO_SLOT)
         ye = O.mm(hp16, wdown, tl, cfg.d, cfg.I)
-        # "peer loads": gather rows back from their owners
-        yes = [None] * world
-        dist.all_gather_object(yes, ye)
+        # return: the owner adds wt * (expert output row) over the pairs of a token it holds, in j order,
+        # and leaves one fp16 partial row per (source rank, token); the home rank adds the partial rows
+        # of the owning ranks in ascending rank order
+        recs = [None] * world
+        dist.all_gather_object(recs, (rank, owner.ravel(), dest_row.ravel(), np.repeat(np.arange(T_local), cfg.K), wt.ravel()))
+        part = np.zeros((world, T_local, cfg.d), np.float32)
+        for s, ow, drow, tok, w in recs:
+            for i in np.nonzero(ow == rank)[0]:       # ascending pair index = (token, j) order
+                part[s, tok[i]] = part[s, tok[i]] + np.float32(w[i]) * ye[drow[i]]
+        parts = [None] * world
+        dist.all_gather_object(parts, part.astype(np.float16))
         h = np.zeros((T_local, cfg.d), np.float32)
-        for j in range(cfg.K):
-            rows = np.stack([yes[o][r] for o, r in zip(owner[:, j], dest_row[:, j])])
-            h += wt[:, j:j + 1] * rows
+        for g in range(world):
+            sel = dests[:, g]
+            h[sel] += parts[g][rank][sel].astype(np.float32)
         err = np.abs(h - full.h[lo:hi, 0])
         assert np.all(err <= 1e-3 + 2e-2 * np.abs(full.h[lo:hi, 0])), err.max()
         q.put((rank, "ok", float(err.max())))
