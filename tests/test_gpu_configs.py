@@ -10,6 +10,31 @@ pytestmark = pytest.mark.gpu
 RTOL_OUT, ATOL_OUT = 2e-2, 1e-3
 
 
+def test_c1_token_order_and_residual_properties(ctx, mc, synth):
+    """Full-size 30B-A3B shape, no oracle involved: a token's output does not depend on where the token
+    sits in the batch (bit-exact under a permutation of the tokens), and the layer adds its result to
+    whatever the residual stream h held (one rounded fp32 addition per element)."""
+    cfg = synth.CONFIGS["c1"]
+    inp = synth.layer_inputs(cfg, 3)
+    T, K, E, d = cfg.T, cfg.K, cfg.E, cfg.d
+    wgu, wdown = ctx.upload(inp.wgu), ctx.upload(inp.wdown)
+
+    def run(proj, x16, h0=None):
+        h = ctx.upload(h0) if h0 is not None else ctx.zeros(T * d * 4)
+        ctx.layer(rows=T, d=d, experts=E, topk=K, inter=cfg.I, shared=0, pstride=cfg.pstride, hc=1,
+                  proj=ctx.upload(proj), x16=ctx.upload(x16), wgu=wgu, wdown=wdown, h=h)
+        ctx.flush()
+        return h.read(np.float32, (T, d))
+
+    base = run(inp.proj, inp.x16)
+    assert np.isfinite(base).all() and np.abs(base).max() > 0
+    perm = np.random.default_rng(11).permutation(T)
+    moved = run(np.ascontiguousarray(inp.proj[perm]), np.ascontiguousarray(inp.x16[perm]))
+    assert np.array_equal(moved, base[perm])
+    h0 = np.random.default_rng(12).standard_normal((T, d)).astype(np.float32)
+    assert np.array_equal(run(inp.proj, inp.x16, h0), h0 + base)
+
+
 def test_c2_80b_shape_full_size(ctx, mc, synth, oracle):
     """T=16384, d=2048, E=512, top-10, I=512, shared S=512 against the full CPU oracle, plus the
     size-independent properties of the path."""
