@@ -429,6 +429,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--flags", type=int, default=0, help="MOE_LAYER_* flags passed to moe_cuda_layer")
     ap.add_argument("--micro-batches", type=int, default=0, help="expert parallel: token slices per layer (0 = automatic)")
+    ap.add_argument("--ep-transfer", type=int, default=0, help="expert parallel: 0 automatic, 1 one row per pair, 2 one row per owning GPU")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -1,7 +1,7 @@
 """Expert-parallel leg of bench.py (N > 1 GPUs of one box, one rank per GPU).
 
 Weak scaling: every rank brings T=4096 tokens of its own (global batch 4096*N) and owns E/N experts;
-a token row is dispatched once per destination GPU and one partial output row returns per owning GPU."""
+rows cross NVLink once per (token, owning GPU) up to 4 GPUs and once per (token, expert) pair beyond."""
 from __future__ import annotations
 
 import dataclasses
@@ -29,7 +29,8 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
 
     uid = [mc.ep_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
-    ctx.ep_init(uid[0], rank, world, E, K, d, I, T, args.micro_batches)
+    ctx.ep_init(uid[0], rank, world, E, K, d, I, T, args.micro_batches, args.ep_transfer)
+    per_gpu = args.ep_transfer == 2 or (args.ep_transfer == 0 and world <= 4)
     d_wgu, d_wdown = ctx.upload(wgu), ctx.upload(wdown)
     d_proj, d_x = ctx.upload(proj), ctx.upload(x16)
     d_h = ctx.zeros(T * d * 4)
@@ -111,8 +112,11 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
         gemm1_flops = T * K * 4 * d * I   # per rank: on average every rank receives T*K rows
         tf1 = gemm1_flops / (stage_ms["gate_up"] * 1e-3) / 1e12
         tf2 = (gemm1_flops / 2) / (stage_ms["down"] * 1e-3) / 1e12
-        disp_bytes = remote_rows * d * 2 + remote_pairs * 4   # rows once per GPU + one 4-byte record per pair
-        ret_bytes = remote_rows * d * 2                       # one fp16 partial row per (token, owning GPU)
+        if per_gpu:
+            disp_bytes = remote_rows * d * 2 + remote_pairs * 12  # rows once per GPU + 4- and 8-byte records per pair
+            ret_bytes = remote_rows * d * 2                       # one fp16 partial row per (token, owning GPU)
+        else:
+            disp_bytes = ret_bytes = remote_pairs * d * 2         # one row per (token, expert) pair each way
         gbs = lambda b, m: b / (m * 1e-3) / 1e9 if m > 0 else None
         out = {
             "metric": METRIC, "value": T * world / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
@@ -131,7 +135,8 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
                        "peak_GB/s": nv_peak,
                        "dispatch_frac": gbs(disp_bytes, stage_ms["scatter"]) / nv_peak,
                        "return_frac": gbs(ret_bytes, stage_ms["combine"]) / nv_peak,
-                       "note": "scatter stage = row send (once per destination GPU) + record scatter + barrier; combine stage = peer loads of one partial row per owning GPU (the owner-side partial sums sit in the down stage)"},
+                       "transfer": "per GPU" if per_gpu else "per pair",
+                       "note": "per GPU: scatter stage = row send (once per destination GPU) + record scatter + barrier, combine stage = peer loads of one partial row per owning GPU (the owner-side partial sums sit in the down stage); per pair: scatter stage = peer-store scatter + barrier, combine stage = peer-load gather"},
             "stages_rank0_ms": {"route": stage_ms["route"], "counts all-gather + plan": stage_ms["scan"],
                                 "scatter + dispatch + barrier": stage_ms["scatter"], "gate_up": stage_ms["gate_up"],
                                 "down": stage_ms["down"], "barrier": stage_ms["shared"],

@@ -198,12 +198,14 @@ void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
  *      reference, which keeps all experts of a layer on one device,
  *      src/qwen.c:235-246) ------------------------------------------------
  * One process per GPU.  Rank g owns experts [g*E/G, (g+1)*E/G) and passes only
- * their weights; every rank passes its own tokens.  Dispatch: each token row
- * is stored once into the receive buffer of every GPU that owns one of its
- * experts, plus one 4-byte record per (token, expert) pair into the owner's
- * source-row table, through which the owner's gate_up product gathers its
- * operand; return: the combine kernel loads each expert-output row from its
- * owner.  All of it is plain peer stores / loads over NVLink; the per-expert counts and the three rendezvous points per layer are
+ * their weights; every rank passes its own tokens.  Dispatch is fused into the
+ * scatter (peer stores of each pair's row into the owner's expert-contiguous
+ * buffer) and return into the combine (peer loads of each pair's output row);
+ * or, with MOE_EP_TRANSFER_PER_GPU, each token row is stored once into the
+ * receive buffer of every GPU that owns one of its experts plus small records
+ * per pair, the owner's gate_up product gathers through those records, and the
+ * owner returns one weighted partial row per token.  All of it is plain peer
+ * stores / loads over NVLink; the per-expert counts and the three rendezvous points per layer are
  * flag exchanges over the same peer memory with bounded waits (a rank that
  * stops coming ends the others' call with MOE_ERR_TIMEOUT after 2 s).  NCCL is
  * needed once, at moe_cuda_ep_init, to hand round the memory handles. */
@@ -212,7 +214,11 @@ typedef struct moe_cuda_ep_cfg_t {
     uint32_t max_rows;                /* most tokens any rank will pass in one call */
     uint32_t micro_batches;           /* 1 or 2 slices of the local tokens that pipeline NVLink transfers against
                                          the products; 0 = automatic (2 from 4 ranks on) */
+    uint32_t transfer;                /* MOE_EP_TRANSFER_*: what crosses NVLink */
 } moe_cuda_ep_cfg_t;
+#define MOE_EP_TRANSFER_AUTO 0u     /* PER_GPU up to 4 ranks, PER_PAIR beyond (measured crossover on B200) */
+#define MOE_EP_TRANSFER_PER_PAIR 1u /* one row per (token, expert) pair each way, written into / read from the owner's expert-contiguous buffers */
+#define MOE_EP_TRANSFER_PER_GPU 2u  /* one row per (token, owning GPU) each way: the owner gathers its operand through a source-row table and returns one weighted partial row per token */
 /* 128 bytes of NCCL unique id: call on one rank, hand the bytes to all. */
 int moe_cuda_ep_unique_id(void *out128);
 /* Rows of each rank's expert-contiguous buffers: sized for the worst case

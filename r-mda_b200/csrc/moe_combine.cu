@@ -32,10 +32,10 @@ moe_combine_kernel(moe_combine_args a) {
     __shared__ uint32_t s_mask, s_terms;
     uint32_t r = blockIdx.x;
     const YT *y = reinterpret_cast<const YT *>(a.y);
-    if (PEER) {
-        // Expert-parallel: every GPU that owns some of the token's experts has already summed
-        // wt * row over those experts (moe_ep_partial_kernel); one such partial row per GPU comes
-        // over NVLink and the partial rows are added in ascending GPU order.
+    if (PEER && a.per_gpu) {
+        // Expert-parallel, one row per owning GPU: every GPU that owns some of the token's experts has
+        // already summed wt * row over those experts (moe_ep_partial_kernel); one such partial row per
+        // GPU comes over NVLink and the partial rows are added in ascending GPU order.
         if (threadIdx.x == 0) s_mask = 0;
         __syncthreads();
         if (threadIdx.x < a.topk) {
@@ -53,6 +53,9 @@ moe_combine_kernel(moe_combine_args a) {
             s_terms = n;
         }
     } else if (threadIdx.x < a.topk) {
+        if (PEER) {  // expert-parallel, one row per pair: read from the GPU that owns the expert, over NVLink
+            s_y[threadIdx.x] = reinterpret_cast<const YT *>(a.y_peers[a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank]);
+        }
         s_slot[threadIdx.x] = a.slot[(size_t)r * a.topk + threadIdx.x];
         s_wt[threadIdx.x] = a.wt[(size_t)r * a.topk + threadIdx.x];
     }
@@ -65,7 +68,7 @@ moe_combine_kernel(moe_combine_args a) {
         s_f[7] = a.sh != NULL ? moe_sigmoid(a.proj[(size_t)r * a.pstride + a.sg_off]) : 0.0f;  // :35
     }
     __syncthreads();
-    const uint32_t terms = PEER ? s_terms : a.topk;
+    const uint32_t terms = (PEER && a.per_gpu) ? s_terms : a.topk;
     float sg = s_f[7];
     float4 keep[NORM ? CB_MAXV : 1];
     float ss = 0.0f;
@@ -147,7 +150,8 @@ void moe_overlap_prepare_combine(moe_cuda_ctx *c) {
 
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a) {
     if (!MOE_LIVE(c)) return;
-    MOE_REQUIRE(c, a.y_peers != NULL || (a.wt != NULL && a.slot != NULL && a.y != NULL), "combine: null buffer");
+    MOE_REQUIRE(c, (a.y_peers != NULL && a.per_gpu) || (a.wt != NULL && a.slot != NULL && (a.y != NULL || a.y_peers != NULL)),
+                "combine: null buffer");
     MOE_REQUIRE(c, a.y_peers == NULL || (a.idx != NULL && a.experts_per_rank >= 1), "combine: peer rows need idx");
     MOE_REQUIRE(c, a.h != NULL || a.y16 != NULL, "combine: no output");
     MOE_REQUIRE(c, a.sh == NULL || a.proj != NULL, "combine: shared term needs proj");

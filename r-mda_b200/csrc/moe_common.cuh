@@ -141,12 +141,14 @@ struct moe_combine_args {
     float eps;
     uint32_t rows, d, topk, pstride, sg_off, inj_stride, inj_off, hc;
     bool y_is_f16;
-    // expert-parallel: GPU g = idx[r,j] / experts_per_rank holds, in y_peers[g] at row src_base + r,
-    // the token's weighted sum over its experts there (fp16); wt, slot and y are then unused
+    // expert-parallel: GPU g = idx[r,j] / experts_per_rank holds row j of the token in y_peers[g] at
+    // row slot[r,j]; or, with per_gpu, at row src_base + r the token's weighted sum over all its
+    // experts there (fp16; wt, slot and y are then unused)
     const uint32_t *idx;
     const void *const *y_peers;
     uint32_t experts_per_rank;
     uint32_t src_base;
+    bool per_gpu;
 };
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a);
 void moe_overlap_prepare_combine(moe_cuda_ctx *c);

@@ -5,19 +5,22 @@
 // single-GPU layer's.
 //
 // The two all-to-alls are fused into the kernels on either side of them instead
-// of being library calls:
-//   dispatch: a token row crosses NVLink once per destination GPU, however many
-//             of its experts live there: the send kernel stores it into that
-//             GPU's receive buffer (slot = source rank, token), and the scatter
-//             kernel stores, for every (token, expert) pair, only a 4-byte record
-//             into the owner's source-row table; the owner's gate_up product
-//             gathers its operand rows through that table;
-//   return:   the same the other way round: the owner sums wt * (expert output
-//             row) over the token's experts it holds (moe_ep_partial_kernel, from
-//             8-byte records the scatter kernel stored beside the source-row
-//             records) and the home GPU's combine kernel loads that one fp16
-//             partial row per owning GPU (peer loads over NVLink), adding the
-//             partial rows in ascending GPU order.
+// of being library calls, in one of two schemes (moe_cuda_ep_cfg_t.transfer):
+//   per pair: dispatch = the scatter kernel writes each (token, expert) pair's row
+//             straight into the owning GPU's expert-contiguous buffer (peer stores
+//             over NVLink); return = the combine kernel gathers each pair's output
+//             row straight from the owning GPU's buffer (peer loads);
+//   per GPU:  a token row crosses NVLink once per destination GPU, however many of
+//             its experts live there: the send kernel stores it into that GPU's
+//             receive buffer (slot = source rank, token), the scatter kernel stores,
+//             for every pair, only a 4-byte record into the owner's source-row
+//             table, and the owner's gate_up product gathers its operand rows
+//             through that table.  The same the other way round: the owner sums
+//             wt * (expert output row) over the token's experts it holds
+//             (moe_ep_partial_kernel, from 8-byte records the scatter kernel stored
+//             beside the source-row records) and the home GPU's combine kernel
+//             loads that one fp16 partial row per owning GPU, adding the partial
+//             rows in ascending GPU order.
 // Peer buffers are plain cudaMalloc memory mapped with CUDA IPC; all accesses
 // are ordinary ld/st (no multimem, no TMA from peer memory: the grouped
 // products only ever read local HBM).  The per-expert counts travel the same way
@@ -27,7 +30,9 @@
 // once, at set-up, to exchange the IPC handles.
 //
 // With top-8 routing over 8 GPUs a token has 7 remote expert copies but only 4.6
-// distinct remote GPUs on average; over 2 GPUs 4 copies but 1 GPU.
+// distinct remote GPUs on average; over 2 GPUs 4 copies but 1 GPU.  The per-GPU
+// scheme pays for the saved bytes with the owner-side sums and a gathering
+// product; it is the default up to 4 GPUs, where it measured faster.
 //
 // Row order inside an expert is (source rank, token index); with contiguous
 // token blocks per rank that is the global token order, so the permutation is
@@ -91,10 +96,15 @@ struct moe_ep_state {
     uint32_t nmb;         // micro-batches: the local tokens are cut in nmb parts that pipeline transfer against products
     uint32_t mcap;        // rows of the expert-contiguous buffers of ONE micro-batch
     uint32_t cap;         // token rows one rank may send per micro-batch
-    __half *xr, *part, *ye, *hp16;       // [nmb * world * cap x d] received rows, the same shape of partial output rows; local only: [nmb * mcap x d], [nmb * mcap x inter]
-    void *xr_peer[MOE_EP_MAX_WORLD];     // every rank's xr as mapped here (own entry = local pointer)
-    void *part_peer[MOE_EP_MAX_WORLD];
-    void **xr_peer_dev[EP_MAX_MB], **part_peer_dev[EP_MAX_MB];  // per micro-batch: each rank's buffer of that micro-batch
+    bool per_gpu;         // transfer scheme: rows cross NVLink once per (token, GPU) instead of once per (token, expert)
+    uint32_t in_rows;     // rows per micro-batch of the two peer-visible buffers: world * cap (per_gpu) or mcap
+    // xin: peer-visible operand rows (per_gpu: received rows, slot = (source rank, token); else expert-contiguous);
+    // yout: peer-visible result rows (per_gpu: one partial row per received token; else the down product's output);
+    // ye: the down product's output when it is not yout (per_gpu only); hp16 [nmb * mcap x inter]
+    __half *xin, *yout, *ye, *hp16;
+    void *xin_peer[MOE_EP_MAX_WORLD];     // every rank's xin as mapped here (own entry = local pointer)
+    void *yout_peer[MOE_EP_MAX_WORLD];
+    void **xin_peer_dev[EP_MAX_MB], **yout_peer_dev[EP_MAX_MB];  // per micro-batch: each rank's buffer of that micro-batch
     void **srow_peer_dev[EP_MAX_MB];     // per micro-batch: each rank's source-row table (inside its sync buffer)
     void **ret_peer_dev[EP_MAX_MB];      // per micro-batch: each rank's return-record table (inside its sync buffer)
     uint32_t *src_row[EP_MAX_MB];        // own tables: expert-contiguous row -> row of xr (~0: padding)
@@ -145,11 +155,11 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
     if (c->stream != NULL) cudaStreamSynchronize(c->stream);
     for (int r = 0; r < ep->world; r += 1) {
         if (r == ep->rank) continue;
-        if (ep->xr_peer[r] != NULL) cudaIpcCloseMemHandle(ep->xr_peer[r]);
-        if (ep->part_peer[r] != NULL) cudaIpcCloseMemHandle(ep->part_peer[r]);
+        if (ep->xin_peer[r] != NULL) cudaIpcCloseMemHandle(ep->xin_peer[r]);
+        if (ep->yout_peer[r] != NULL) cudaIpcCloseMemHandle(ep->yout_peer[r]);
         if (ep->sync_peer[r] != NULL) cudaIpcCloseMemHandle(ep->sync_peer[r]);
     }
-    void *mine[] = {ep->xr, ep->part, ep->ye, ep->hp16, ep->xr_peer_dev[0], ep->part_peer_dev[0], ep->xr_peer_dev[1], ep->part_peer_dev[1],
+    void *mine[] = {ep->xin, ep->yout, ep->ye, ep->hp16, ep->xin_peer_dev[0], ep->yout_peer_dev[0], ep->xin_peer_dev[1], ep->yout_peer_dev[1],
                     ep->srow_peer_dev[0], ep->srow_peer_dev[1], ep->ret_peer_dev[0], ep->ret_peer_dev[1], ep->sync_peer_dev, ep->sync, ep->dst_off[0], ep->dst_off[1], ep->tiles[0], ep->tiles[1], ep->count[0],
                     ep->count[1], ep->idx, ep->slot, ep->bar, ep->wt};
     if (ep->side != NULL) {
@@ -176,7 +186,7 @@ __global__ void moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32
                                    uint32_t table_off, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
                                    uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status);
 
-__global__ void moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xr_peers,
+__global__ void moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xin_peers,
                                    uint32_t rows, uint32_t topk, uint32_t d8, uint32_t el, uint32_t world, uint32_t src_base);
 
 __global__ void moe_ep_partial_kernel(const uint2 *__restrict__ ret_tab, const uint4 *__restrict__ ye, uint4 *__restrict__ part,
@@ -200,6 +210,7 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
         return;
     }
     MOE_REQUIRE(c, cfg->micro_batches <= EP_MAX_MB, "ep_init: micro_batches %u > %d", cfg->micro_batches, EP_MAX_MB);
+    MOE_REQUIRE(c, cfg->transfer <= MOE_EP_TRANSFER_PER_GPU, "ep_init: transfer %u", cfg->transfer);
     // 0 = automatic: with 4 or more ranks most rows cross NVLink, and cutting the tokens in two lets one
     // half's transfers run under the other half's products
     uint32_t nmb = cfg->micro_batches != 0 ? cfg->micro_batches : (world >= 4 ? 2u : 1u);
@@ -228,16 +239,22 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     const size_t ret_words0 = (srow_words0 + (size_t)nmb * mcap + 1u) & ~(size_t)1u;  // 8-byte records
     const size_t ret_words = (size_t)world * rows_mb * K * 2u;                          // per micro-batch
     const size_t sync_words = ret_words0 + (size_t)nmb * ret_words;
-    ep->xr = (__half *)moe_cuda_alloc(c, (size_t)nmb * world * rows_mb * cfg->d * 2);
-    ep->part = (__half *)moe_cuda_alloc(c, (size_t)nmb * world * rows_mb * cfg->d * 2);
-    ep->ye = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->d * 2);
+    // Measured on B200 (30B-A3B shape, 4096 tokens per GPU): once-per-GPU transfers win at 2 GPUs
+    // (0.512 against 0.594 ms per layer) and at 4 (0.610 against 0.642), per-pair transfers at 8
+    // (0.672 against 0.754: 4.6 of 7 rows still travel, and the owner-side sums and the gathering
+    // product cost more than the saved bytes).
+    ep->per_gpu = cfg->transfer == MOE_EP_TRANSFER_AUTO ? world <= 4 : cfg->transfer == MOE_EP_TRANSFER_PER_GPU;
+    ep->in_rows = ep->per_gpu ? (uint32_t)world * rows_mb : mcap;
+    ep->xin = (__half *)moe_cuda_alloc(c, (size_t)nmb * ep->in_rows * cfg->d * 2);
+    ep->yout = (__half *)moe_cuda_alloc(c, (size_t)nmb * ep->in_rows * cfg->d * 2);
+    ep->ye = ep->per_gpu ? (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->d * 2) : NULL;
     ep->hp16 = (__half *)moe_cuda_alloc(c, (size_t)nmb * mcap * cfg->inter * 2);
     ep->sync = (uint32_t *)moe_cuda_alloc(c, sync_words * 4);
     ep->sync_peer_dev = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
     for (uint32_t m = 0; m < nmb; m += 1) {
-        ep->xr_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+        ep->xin_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
         ep->srow_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
-        ep->part_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
+        ep->yout_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
         ep->ret_peer_dev[m] = (void **)moe_cuda_alloc(c, MOE_EP_MAX_WORLD * sizeof(void *));
         ep->dst_off[m] = (uint32_t *)moe_cuda_alloc(c, E * 4);
         ep->tiles[m] = (uint32_t *)moe_cuda_alloc(c, (size_t)(mcap / MOE_TILE) * 4);
@@ -265,13 +282,13 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->bar, 0, 256, c->stream));
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->sync, 0, sync_words * 4, c->stream));
 
-    // Exchange the IPC handles of xr, part and sync through the communicator itself.
+    // Exchange the IPC handles of xin, yout and sync through the communicator itself.
     struct Handles {
-        cudaIpcMemHandle_t xr, part, sync;
+        cudaIpcMemHandle_t xin, yout, sync;
     };
     Handles mine;
-    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.xr, ep->xr));
-    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.part, ep->part));
+    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.xin, ep->xin));
+    MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.yout, ep->yout));
     MOE_CUDA_TRY(c, cudaIpcGetMemHandle(&mine.sync, ep->sync));
     Handles *d_all = (Handles *)moe_cuda_alloc(c, sizeof(Handles) * (size_t)world);
     if (d_all == NULL) return;
@@ -283,27 +300,27 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     cudaFree(d_all);
     for (int r = 0; r < world; r += 1) {
         if (r == rank) {
-            ep->xr_peer[r] = ep->xr;
-            ep->part_peer[r] = ep->part;
+            ep->xin_peer[r] = ep->xin;
+            ep->yout_peer[r] = ep->yout;
             ep->sync_peer[r] = ep->sync;
             continue;
         }
-        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->xr_peer[r], all[r].xr, cudaIpcMemLazyEnablePeerAccess));
-        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->part_peer[r], all[r].part, cudaIpcMemLazyEnablePeerAccess));
+        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->xin_peer[r], all[r].xin, cudaIpcMemLazyEnablePeerAccess));
+        MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->yout_peer[r], all[r].yout, cudaIpcMemLazyEnablePeerAccess));
         MOE_CUDA_TRY(c, cudaIpcOpenMemHandle(&ep->sync_peer[r], all[r].sync, cudaIpcMemLazyEnablePeerAccess));
     }
-    for (uint32_t m = 0; m < nmb; m += 1) {  // micro-batch m: row m * world * cap of xr and part, tables m
+    for (uint32_t m = 0; m < nmb; m += 1) {  // micro-batch m: row m * in_rows of xin and yout, tables m
         void *xt[MOE_EP_MAX_WORLD] = {}, *yt[MOE_EP_MAX_WORLD] = {}, *st[MOE_EP_MAX_WORLD] = {}, *rt[MOE_EP_MAX_WORLD] = {};
         for (int r = 0; r < world; r += 1) {
-            xt[r] = (__half *)ep->xr_peer[r] + (size_t)m * world * rows_mb * cfg->d;
-            yt[r] = (__half *)ep->part_peer[r] + (size_t)m * world * rows_mb * cfg->d;
+            xt[r] = (__half *)ep->xin_peer[r] + (size_t)m * ep->in_rows * cfg->d;
+            yt[r] = (__half *)ep->yout_peer[r] + (size_t)m * ep->in_rows * cfg->d;
             st[r] = (uint32_t *)ep->sync_peer[r] + srow_words0 + (size_t)m * mcap;
             rt[r] = (uint32_t *)ep->sync_peer[r] + ret_words0 + (size_t)m * ret_words;
         }
         ep->src_row[m] = ep->sync + srow_words0 + (size_t)m * mcap;
         ep->ret_tab[m] = (uint2 *)(ep->sync + ret_words0 + (size_t)m * ret_words);
-        MOE_CUDA_TRY(c, cudaMemcpy(ep->xr_peer_dev[m], xt, sizeof(xt), cudaMemcpyHostToDevice));
-        MOE_CUDA_TRY(c, cudaMemcpy(ep->part_peer_dev[m], yt, sizeof(yt), cudaMemcpyHostToDevice));
+        MOE_CUDA_TRY(c, cudaMemcpy(ep->xin_peer_dev[m], xt, sizeof(xt), cudaMemcpyHostToDevice));
+        MOE_CUDA_TRY(c, cudaMemcpy(ep->yout_peer_dev[m], yt, sizeof(yt), cudaMemcpyHostToDevice));
         MOE_CUDA_TRY(c, cudaMemcpy(ep->srow_peer_dev[m], st, sizeof(st), cudaMemcpyHostToDevice));
         MOE_CUDA_TRY(c, cudaMemcpy(ep->ret_peer_dev[m], rt, sizeof(rt), cudaMemcpyHostToDevice));
     }
@@ -408,7 +425,7 @@ moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_
 // buffer of every GPU that owns at least one of the token's experts (its own included: the
 // product gathers all its operand rows from the receive buffer), at row src_base + token.
 __global__ void __launch_bounds__(256)
-moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xr_peers,
+moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xin_peers,
                    uint32_t rows, uint32_t topk, uint32_t d8, uint32_t el, uint32_t world, uint32_t src_base) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -428,7 +445,7 @@ moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x
                 if (ci < d8) v[i] = __ldg(src + ci);
             }
             for (uint32_t mk = mask; mk != 0; mk &= mk - 1u) {
-                uint4 *dst = xr_peers[__ffs((int)mk) - 1] + (size_t)(src_base + r) * d8;
+                uint4 *dst = xin_peers[__ffs((int)mk) - 1] + (size_t)(src_base + r) * d8;
 #pragma unroll
                 for (uint32_t i = 0; i < 8; i += 1) {
                     const uint32_t ci = c0 + i * 32u + lane;
@@ -531,10 +548,12 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
     mark(0);
     for (uint32_t m = 0; m < nmb; m += 1) {
         moe_cuda_fill(c, ep->tiles[m], (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
-        // padding rows of used tiles read as zero; peers write the live entries after the first barrier
-        moe_cuda_fill(c, ep->src_row[m], (size_t)mcap * 4, 0xffffffffu);
-        // return records: ~0 ends a token's list
-        moe_cuda_fill(c, ep->ret_tab[m], (size_t)ep->world * ep->cap * K * 8, 0xffffffffu);
+        if (ep->per_gpu) {
+            // padding rows of used tiles read as zero; peers write the live entries after the first barrier
+            moe_cuda_fill(c, ep->src_row[m], (size_t)mcap * 4, 0xffffffffu);
+            // return records: ~0 ends a token's list
+            moe_cuda_fill(c, ep->ret_tab[m], (size_t)ep->world * ep->cap * K * 8, 0xffffffffu);
+        }
     }
     uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)((R + 7u) / 8u + 1u) * E * 4);
     if (hist == NULL) return;
@@ -568,12 +587,20 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             // stagger: this slice's rows go out once the first slice's are on their way, under its products
             cudaStreamWaitEvent(c->stream, ep->ev_disp, 0);
         }
-        // dispatch: each row once per destination GPU, then the 4-byte records of every (token, expert) pair
-        if (rows != 0) {
+        __half *xin_m = ep->xin + (size_t)m * ep->in_rows * d, *yout_m = ep->yout + (size_t)m * ep->in_rows * d;
+        __half *ye_m = ep->per_gpu ? ep->ye + (size_t)m * mcap * d : yout_m;
+        if (rows != 0 && !ep->per_gpu) {
+            // dispatch fused into the scatter: every pair's row goes straight into its owner's expert-contiguous buffer
+            moe_launch_place(c, idx + (size_t)row0 * K, ep->dst_off[m], hist + (size_t)(row0 / 8u) * E,
+                             (const __half *)L->x16 + (size_t)row0 * d, xin_m, slot + (size_t)row0 * K, rows, K, d / 8u, E,
+                             ep->xin_peer_dev[m], ep->el);
+        }
+        // dispatch: each row once per destination GPU, then the records of every (token, expert) pair
+        if (rows != 0 && ep->per_gpu) {
             const uint32_t src_base = (uint32_t)ep->rank * ep->cap;
             moe_ep_send_kernel<<<(rows + 7u) / 8u, 256, 0, c->stream>>>(
                 idx + (size_t)row0 * K, (const uint4 *)((const __half *)L->x16 + (size_t)row0 * d),
-                (uint4 *const *)ep->xr_peer_dev[m], rows, K, d / 8u, ep->el, (uint32_t)ep->world, src_base);
+                (uint4 *const *)ep->xin_peer_dev[m], rows, K, d / 8u, ep->el, (uint32_t)ep->world, src_base);
             c->launches += 1;
             moe_launch_place(c, idx + (size_t)row0 * K, ep->dst_off[m], hist + (size_t)(row0 / 8u) * E, L->x16, NULL,
                              slot + (size_t)row0 * K, rows, K, d / 8u, E, NULL, ep->el, NULL,
@@ -585,30 +612,28 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
                                                        (uint32_t)ep->rank, site + 1u, ep->epoch, c->dev_status_dev);  // all rows landed
         c->launches += 1;
         if (m == 0) mark(3);
-        moe_launch_mm(c, MOE_MM_SWIGLU_F16, ep->xr + (size_t)m * ep->world * ep->cap * d, L->wgu, ep->hp16 + (size_t)m * mcap * I,
-                      NULL, ep->tiles[m], mcap, 2u * I, d, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el,
-                      (uint32_t)ep->world * ep->cap, true, ep->src_row[m]);
+        moe_launch_mm(c, MOE_MM_SWIGLU_F16, xin_m, L->wgu, ep->hp16 + (size_t)m * mcap * I, NULL, ep->tiles[m], mcap, 2u * I, d,
+                      MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, ep->in_rows, true, ep->per_gpu ? ep->src_row[m] : NULL);
         if (m == 0) mark(4);
-        moe_launch_mm(c, MOE_MM_F16, ep->hp16 + (size_t)m * mcap * I, L->wdown, ep->ye + (size_t)m * mcap * d, NULL,
+        moe_launch_mm(c, MOE_MM_F16, ep->hp16 + (size_t)m * mcap * I, L->wdown, ye_m, NULL,
                       ep->tiles[m], mcap, d, I, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);
-        {   // return, owner side: one weighted partial row per received token
+        if (ep->per_gpu) {  // return, owner side: one weighted partial row per received token
             const uint32_t slots = (uint32_t)ep->world * ep->cap;
             const uint32_t units = slots * ((d / 8u + 127u) / 128u);  // one warp per (slot, 2 KB piece)
             moe_ep_partial_kernel<<<(units + 7u) / 8u, 256, 0, c->stream>>>(
-                ep->ret_tab[m], (const uint4 *)(ep->ye + (size_t)m * mcap * d),
-                (uint4 *)(ep->part + (size_t)m * ep->world * ep->cap * d), slots, K, d / 8u);
+                ep->ret_tab[m], (const uint4 *)ye_m, (uint4 *)yout_m, slots, K, d / 8u);
             c->launches += 1;
         }
         if (m == 0) mark(5);
         moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
-                                                       (uint32_t)ep->rank, site + 2u, ep->epoch, c->dev_status_dev);  // all partial rows written
+                                                       (uint32_t)ep->rank, site + 2u, ep->epoch, c->dev_status_dev);  // all result rows written
         c->launches += 1;
         if (m == 0) mark(6);
         if (rows != 0) {
             moe_combine_args a = {};
             a.wt = wt + (size_t)row0 * K;
             a.slot = slot + (size_t)row0 * K;
-            a.y = ep->ye + (size_t)m * mcap * d;
+            a.y = ye_m;
             a.proj = L->proj + (size_t)row0 * L->pstride;
             a.inj = L->inj != NULL ? L->inj + (size_t)row0 * L->inj_stride : NULL;
             a.h = L->h != NULL ? L->h + (size_t)row0 * L->hc * d : NULL;
@@ -625,9 +650,10 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             a.hc = L->hc;
             a.y_is_f16 = true;
             a.idx = idx + (size_t)row0 * K;
-            a.y_peers = (const void *const *)ep->part_peer_dev[m];
+            a.y_peers = (const void *const *)ep->yout_peer_dev[m];
             a.experts_per_rank = ep->el;
             a.src_base = (uint32_t)ep->rank * ep->cap;
+            a.per_gpu = ep->per_gpu;
             moe_launch_combine(c, a);  // return all-to-all fused into the gather: one partial row per owning GPU
         }
         if (m == 0) mark(7);

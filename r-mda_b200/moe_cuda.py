@@ -61,7 +61,7 @@ class Layer(C.Structure):
 
 
 class EpCfg(C.Structure):
-    _fields_ = [(n, C.c_uint32) for n in ("experts", "topk", "d", "inter", "max_rows", "micro_batches")]
+    _fields_ = [(n, C.c_uint32) for n in ("experts", "topk", "d", "inter", "max_rows", "micro_batches", "transfer")]
 
 
 _lib = None
@@ -273,10 +273,11 @@ class Ctx:
             setattr(L, k, _ptr(v) if isinstance(v, DevBuf) or v is None else v)
         lib().moe_cuda_layer(self.p, C.byref(L))
 
-    def ep_init(self, unique_id: bytes, rank: int, world: int, experts, topk, d, inter, max_rows, micro_batches=0):
+    def ep_init(self, unique_id: bytes, rank: int, world: int, experts, topk, d, inter, max_rows, micro_batches=0,
+                transfer=0):
         assert len(unique_id) == 128
         buf = C.create_string_buffer(unique_id, 128)
-        cfg = EpCfg(experts, topk, d, inter, max_rows, micro_batches)
+        cfg = EpCfg(experts, topk, d, inter, max_rows, micro_batches, transfer)
         lib().moe_cuda_ep_init(self.p, buf, rank, world, C.byref(cfg))
         self.check()
 
