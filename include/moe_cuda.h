@@ -213,7 +213,7 @@ typedef struct moe_cuda_ep_cfg_t {
     uint32_t experts, topk, d, inter; /* global expert count; experts % world == 0, inter % 128 == 0 */
     uint32_t max_rows;                /* most tokens any rank will pass in one call */
     uint32_t micro_batches;           /* 1 or 2 slices of the local tokens that pipeline NVLink transfers against
-                                         the products; 0 = automatic (2 from 4 ranks on) */
+                                         the products; 0 = automatic (2 with per-pair transfers over 4 or more ranks, else 1) */
     uint32_t transfer;                /* MOE_EP_TRANSFER_*: what crosses NVLink */
 } moe_cuda_ep_cfg_t;
 #define MOE_EP_TRANSFER_AUTO 0u     /* PER_GPU up to 4 ranks, PER_PAIR beyond (measured crossover on B200) */

@@ -211,9 +211,16 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     }
     MOE_REQUIRE(c, cfg->micro_batches <= EP_MAX_MB, "ep_init: micro_batches %u > %d", cfg->micro_batches, EP_MAX_MB);
     MOE_REQUIRE(c, cfg->transfer <= MOE_EP_TRANSFER_PER_GPU, "ep_init: transfer %u", cfg->transfer);
-    // 0 = automatic: with 4 or more ranks most rows cross NVLink, and cutting the tokens in two lets one
-    // half's transfers run under the other half's products
-    uint32_t nmb = cfg->micro_batches != 0 ? cfg->micro_batches : (world >= 4 ? 2u : 1u);
+    // Measured on B200 (30B-A3B shape, 4096 tokens per GPU, ms per layer): once-per-GPU transfers win
+    // at 2 GPUs (0.512 against 0.588) and at 4 (0.610 against 0.642), per-pair transfers at 8 (0.672
+    // against 0.754: 4.6 of 7 rows still travel, and the owner-side sums and the gathering product
+    // cost more than the saved bytes).
+    const bool per_gpu = cfg->transfer == MOE_EP_TRANSFER_AUTO ? world <= 4 : cfg->transfer == MOE_EP_TRANSFER_PER_GPU;
+    // micro_batches 0 = automatic: with per-pair transfers over 4 or more ranks most rows cross NVLink,
+    // and cutting the tokens in two lets one half's transfers run under the other half's products
+    // (0.672 against 0.712 at 8 GPUs); with per-GPU transfers one slice measured faster (0.610
+    // against 0.617 at 4 GPUs, 0.512 against 0.572 at 2)
+    uint32_t nmb = cfg->micro_batches != 0 ? cfg->micro_batches : ((world >= 4 && !per_gpu) ? 2u : 1u);
     uint32_t rows_mb = nmb == 1 ? cfg->max_rows : (((cfg->max_rows + 1u) / 2u + 7u) & ~7u);
     uint32_t mcap = moe_cuda_ep_rows((uint32_t)world, rows_mb, cfg->experts, cfg->topk);
     MOE_REQUIRE(c, mcap != 0, "ep_init: buffer rows overflow");
@@ -239,11 +246,7 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     const size_t ret_words0 = (srow_words0 + (size_t)nmb * mcap + 1u) & ~(size_t)1u;  // 8-byte records
     const size_t ret_words = (size_t)world * rows_mb * K * 2u;                          // per micro-batch
     const size_t sync_words = ret_words0 + (size_t)nmb * ret_words;
-    // Measured on B200 (30B-A3B shape, 4096 tokens per GPU): once-per-GPU transfers win at 2 GPUs
-    // (0.512 against 0.594 ms per layer) and at 4 (0.610 against 0.642), per-pair transfers at 8
-    // (0.672 against 0.754: 4.6 of 7 rows still travel, and the owner-side sums and the gathering
-    // product cost more than the saved bytes).
-    ep->per_gpu = cfg->transfer == MOE_EP_TRANSFER_AUTO ? world <= 4 : cfg->transfer == MOE_EP_TRANSFER_PER_GPU;
+    ep->per_gpu = per_gpu;
     ep->in_rows = ep->per_gpu ? (uint32_t)world * rows_mb : mcap;
     ep->xin = (__half *)moe_cuda_alloc(c, (size_t)nmb * ep->in_rows * cfg->d * 2);
     ep->yout = (__half *)moe_cuda_alloc(c, (size_t)nmb * ep->in_rows * cfg->d * 2);

@@ -38,7 +38,8 @@ def main():
         lo, hi = rank * T_local, (rank + 1) * T_local
         uid = [mc.ep_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
-        eff_mb = nmb if nmb else (2 if world >= 4 else 1)
+        per_gpu = transfer == 2 or (transfer == 0 and world <= 4)
+        eff_mb = nmb if nmb else (2 if (world >= 4 and not per_gpu) else 1)   # the library's automatic choice
         r0 = T_local if eff_mb == 1 else min(T_local, ((T_local + 1) // 2 + 7) // 8 * 8)
         # expected rows: inside the owner's buffer of the token's micro-batch, rows of an expert are ordered
         # (source rank, token) -- the single-device order restricted to that micro-batch
