@@ -23,7 +23,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, T_local, fail_rank, q):
+def _worker(rank, world, port, T_local, fail_rank, per_gpu, q):
     sys.path.insert(0, ROOT)
     import dataclasses
     import __graft_entry__ as entry
@@ -56,49 +56,68 @@ def _worker(rank, world, port, T_local, fail_rank, q):
         want_row = (full.slot[lo:hi].astype(np.int64) - full.off[idx].astype(np.int64)
                     + np.array([epp.plan(cnt_all, o)[1] for o in range(world)]).reshape(-1)[idx])
         assert np.array_equal(dest_row, want_row)
-        # dispatch: a row travels once per destination rank into that rank's receive buffer (slot =
-        # source rank, token); every (token, expert) pair travels as a 4-byte record into the owner's
-        # source-row table.  Every rank learns all of it and keeps what is addressed to it.
         mcap = epp.ep_rows(world, T_local, cfg.E, cfg.K)
-        dests = epp.dest_ranks(idx, el, world)
-        assert dests.sum() <= owner.size and np.array_equal(dests.any(1), np.ones(T_local, bool))
-        objs = [None] * world
-        dist.all_gather_object(objs, (rank, dests, x16, owner.ravel(), dest_row.ravel(),
-                                      np.repeat(np.arange(T_local), cfg.K)))
-        xr = np.full((world * T_local, cfg.d), 0x7e00, np.uint16)      # fp16 NaN: a row that never arrived would show
-        have = np.zeros(world * T_local, bool)
-        src_row = np.full(mcap, -1, np.int64)
-        for s, dst, rows_x, ow, drow, tok in objs:
-            sel = dst[:, rank]
-            xr[s * T_local + np.nonzero(sel)[0]] = rows_x[sel]
-            have[s * T_local + np.nonzero(sel)[0]] = True
-            selp = ow == rank
-            assert (src_row[drow[selp]] == -1).all()      # no two pairs land on the same row
-            src_row[drow[selp]] = s * T_local + tok[selp]
-        live = src_row >= 0
-        assert have[src_row[live]].all()                  # every row a record points at was sent
-        xp = np.zeros((mcap, cfg.d), np.uint16)           # what the owner's product gathers
-        xp[live] = xr[src_row[live]]
+        if per_gpu:
+            # dispatch: a row travels once per destination rank into that rank's receive buffer (slot =
+            # source rank, token); every (token, expert) pair travels as a 4-byte record into the owner's
+            # source-row table.  Every rank learns all of it and keeps what is addressed to it.
+            dests = epp.dest_ranks(idx, el, world)
+            assert dests.sum() <= owner.size and np.array_equal(dests.any(1), np.ones(T_local, bool))
+            objs = [None] * world
+            dist.all_gather_object(objs, (rank, dests, x16, owner.ravel(), dest_row.ravel(),
+                                          np.repeat(np.arange(T_local), cfg.K)))
+            xr = np.full((world * T_local, cfg.d), 0x7e00, np.uint16)      # fp16 NaN: a row that never arrived would show
+            have = np.zeros(world * T_local, bool)
+            src_row = np.full(mcap, -1, np.int64)
+            for s, dst, rows_x, ow, drow, tok in objs:
+                sel = dst[:, rank]
+                xr[s * T_local + np.nonzero(sel)[0]] = rows_x[sel]
+                have[s * T_local + np.nonzero(sel)[0]] = True
+                selp = ow == rank
+                assert (src_row[drow[selp]] == -1).all()      # no two pairs land on the same row
+                src_row[drow[selp]] = s * T_local + tok[selp]
+            live = src_row >= 0
+            assert have[src_row[live]].all()                  # every row a record points at was sent
+            xp = np.zeros((mcap, cfg.d), np.uint16)           # what the owner's product gathers
+            xp[live] = xr[src_row[live]]
+        else:
+            # per pair, "peer stores": every rank learns all (owner, row, data) triples and keeps its own
+            objs = [None] * world
+            dist.all_gather_object(objs, (owner.ravel(), dest_row.ravel(), np.repeat(x16, cfg.K, 0)))
+            xp = np.zeros((mcap, cfg.d), np.uint16)
+            for ow, rows, data in objs:
+                sel = ow == rank
+                assert not xp[rows[sel]].any()          # no two pairs land on the same row
+                xp[rows[sel]] = data[sel]
         tl = np.full(mcap // 128, 0xffffffff, np.uint32)
         tl[:len(tiles)] = tiles
         g = O.mm(xp, wgu, tl, 2 * cfg.I, cfg.d)
         hp16 = O.cast_f16(O.swiglu(g, cfg.I, 2 * cfg.I, 0, cfg.I), np.zeros(4, np.uint32), O.NO_SLOT)
         ye = O.mm(hp16, wdown, tl, cfg.d, cfg.I)
-        # return: the owner adds wt * (expert output row) over the pairs of a token it holds, in j order,
-        # and leaves one fp16 partial row per (source rank, token); the home rank adds the partial rows
-        # of the owning ranks in ascending rank order
-        recs = [None] * world
-        dist.all_gather_object(recs, (rank, owner.ravel(), dest_row.ravel(), np.repeat(np.arange(T_local), cfg.K), wt.ravel()))
-        part = np.zeros((world, T_local, cfg.d), np.float32)
-        for s, ow, drow, tok, w in recs:
-            for i in np.nonzero(ow == rank)[0]:       # ascending pair index = (token, j) order
-                part[s, tok[i]] = part[s, tok[i]] + np.float32(w[i]) * ye[drow[i]]
-        parts = [None] * world
-        dist.all_gather_object(parts, part.astype(np.float16))
-        h = np.zeros((T_local, cfg.d), np.float32)
-        for g in range(world):
-            sel = dests[:, g]
-            h[sel] += parts[g][rank][sel].astype(np.float32)
+        if per_gpu:
+            # return: the owner adds wt * (expert output row) over the pairs of a token it holds, in j order,
+            # and leaves one fp16 partial row per (source rank, token); the home rank adds the partial rows
+            # of the owning ranks in ascending rank order
+            recs = [None] * world
+            dist.all_gather_object(recs, (rank, owner.ravel(), dest_row.ravel(), np.repeat(np.arange(T_local), cfg.K), wt.ravel()))
+            part = np.zeros((world, T_local, cfg.d), np.float32)
+            for s, ow, drow, tok, w in recs:
+                for i in np.nonzero(ow == rank)[0]:       # ascending pair index = (token, j) order
+                    part[s, tok[i]] = part[s, tok[i]] + np.float32(w[i]) * ye[drow[i]]
+            parts = [None] * world
+            dist.all_gather_object(parts, part.astype(np.float16))
+            h = np.zeros((T_local, cfg.d), np.float32)
+            for g in range(world):
+                sel = dests[:, g]
+                h[sel] += parts[g][rank][sel].astype(np.float32)
+        else:
+            # per pair, "peer loads": gather each pair's row back from its owner, accumulate in j order
+            yes = [None] * world
+            dist.all_gather_object(yes, ye)
+            h = np.zeros((T_local, cfg.d), np.float32)
+            for j in range(cfg.K):
+                rows = np.stack([yes[o][r] for o, r in zip(owner[:, j], dest_row[:, j])])
+                h += wt[:, j:j + 1] * rows
         err = np.abs(h - full.h[lo:hi, 0])
         assert np.all(err <= 1e-3 + 2e-2 * np.abs(full.h[lo:hi, 0])), err.max()
         q.put((rank, "ok", float(err.max())))
@@ -111,11 +130,11 @@ def _worker(rank, world, port, T_local, fail_rank, q):
             pass
 
 
-def _run(world, T_local, fail_rank=-1):
+def _run(world, T_local, fail_rank=-1, per_gpu=True):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    ps = [ctx.Process(target=_worker, args=(r, world, port, T_local, fail_rank, q)) for r in range(world)]
+    ps = [ctx.Process(target=_worker, args=(r, world, port, T_local, fail_rank, per_gpu, q)) for r in range(world)]
     for p in ps:
         p.start()
     out = [q.get(timeout=120) for _ in range(world)]
@@ -124,13 +143,15 @@ def _run(world, T_local, fail_rank=-1):
     return sorted(out)
 
 
-def test_two_ranks_reproduce_single_gpu_layer():
-    out = _run(2, 96)
+@pytest.mark.parametrize("per_gpu", [True, False], ids=["per_gpu", "per_pair"])
+def test_two_ranks_reproduce_single_gpu_layer(per_gpu):
+    out = _run(2, 96, per_gpu=per_gpu)
     assert [o[1] for o in out] == ["ok", "ok"], out
 
 
-def test_four_ranks_ragged_tokens():
-    out = _run(4, 37)
+@pytest.mark.parametrize("per_gpu", [True, False], ids=["per_gpu", "per_pair"])
+def test_four_ranks_ragged_tokens(per_gpu):
+    out = _run(4, 37, per_gpu=per_gpu)
     assert [o[1] for o in out] == ["ok"] * 4, out
 
 
