@@ -37,12 +37,13 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
 
 
 def build_host(force: bool = False) -> str:
-    """The C mirror of the reference's call sites, compiled as the reference is (gnu17)."""
-    src = os.path.join(PKG, "host", "moe_host.c")
-    deps = [src, os.path.join(PKG, "host", "moe_host.h"), os.path.join(ROOT, "include", "moe_cuda.h")]
+    """The C mirror of the reference's call sites and of its weight path, compiled as the reference is (gnu17)."""
+    srcs = [os.path.join(PKG, "host", "moe_host.c"), os.path.join(PKG, "host", "moe_weights.c")]
+    deps = srcs + [os.path.join(PKG, "host", "moe_host.h"), os.path.join(PKG, "host", "moe_weights.h"),
+                   os.path.join(ROOT, "include", "moe_cuda.h")]
     if force or _stale(HOST_LIB, deps) or _stale(HOST_LIB, [LIB]):
         cmd = ["gcc", "-std=gnu17", "-O2", "-Wall", "-Wextra", "-shared", "-fPIC", "-I", os.path.join(ROOT, "include"),
-               "-o", HOST_LIB, src, "-L", PKG, "-lmoe_cuda", "-Wl,-rpath,$ORIGIN"]
+               "-o", HOST_LIB] + srcs + ["-L", PKG, "-lmoe_cuda", "-lpthread", "-Wl,-rpath,$ORIGIN"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("gcc failed:\n" + r.stdout + r.stderr)
