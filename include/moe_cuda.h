@@ -39,6 +39,7 @@ struct mda_pc_qwen_elem_t { uint32_t rows, n, astride, ao, bo, op; float scale; 
 struct mda_pc_absmax_t { uint32_t n, slot; };                                          /* shader/absmax.comp:6-9 */
 struct mda_pc_cast_t { uint32_t n, slot; };                                            /* shader/cast_f16.comp:14-17 */
 struct mda_pc_qwen_bf16_t { uint32_t n; };                                             /* src/pc.h:273-275 */
+struct mda_pc_kd_bytes_t { uint32_t rows, vocab; };                                    /* src/pc.h:406-409 */
 #endif
 typedef struct mda_pc_moe_route_t moe_pc_route_t;
 typedef struct mda_pc_moe_scan_t moe_pc_scan_t;
@@ -159,6 +160,16 @@ void moe_cuda_cast_f16(moe_cuda_ctx_t *c, const float *src, void *dst, const uin
  * pc.n 32-bit words of two bf16 values each, rewritten in place as fp16 (round
  * to nearest even) right after the host-to-device copy of a layer's weights. */
 void moe_cuda_bf16_to_f16(moe_cuda_ctx_t *c, void *w, struct mda_pc_qwen_bf16_t pc);
+
+/* ---- distillation sink behind the teacher's head --------------------------
+ * shader/kd_bytes.comp (bindings logits, toks, cont, outp; call mda_teach_sink,
+ * src/teach.c:108-128).  logits fp32 [rows x vocab]; toks [vocab x 5] u32: 16
+ * bytes of the token (little-endian in four words) and its length, 0 = no byte
+ * string; cont [rows x 5]: the 16 bytes that follow the row's position and how
+ * many of them count; outp [rows x 16 x 8] entries byte | fp16(p) << 16 -- per
+ * depth the true byte's probability, then the seven most probable other bytes. */
+void moe_cuda_kd_bytes(moe_cuda_ctx_t *c, const float *logits, const uint32_t *toks, const uint32_t *cont,
+                       uint32_t *outp, struct mda_pc_kd_bytes_t pc);
 
 /* ---- the fused layer: mda_qwen_route_rec + mda_qwen_moe_rec from the first
  *      grouped product on (src/qwen.c:788-836, 847-906) in one call --------- */

@@ -184,6 +184,16 @@ def bf16_to_f16(w):
     return out
 
 
+def kd_bytes(logits, toks, cont):
+    """shader/kd_bytes.comp.  logits f32 [rows, vocab], toks u32 [vocab, 5], cont u32 [rows, 5] -> u32 [rows, 16, 8]."""
+    _chk(logits, np.float32, "logits"); _chk(toks, np.uint32, "toks"); _chk(cont, np.uint32, "cont")
+    rows, vocab = logits.shape
+    assert toks.shape == (vocab, 5) and cont.shape == (rows, 5)
+    out = np.empty((rows, 16, 8), np.uint32)
+    lib().moe_ref_kd_bytes(_p(logits), _p(toks), _p(cont), _p(out), C.c_uint32(rows), C.c_uint32(vocab))
+    return out
+
+
 class _Layer(C.Structure):
     _fields_ = [
         ("rows", C.c_uint32), ("d", C.c_uint32), ("experts", C.c_uint32), ("topk", C.c_uint32),

@@ -295,6 +295,78 @@ void moe_ref_bf16_to_f16(uint32_t *w, uint64_t n) {
     }
 }
 
+/* shader/kd_bytes.comp:26-28 */
+static uint32_t kd_byte_at(const uint32_t w[4], uint32_t i) {
+    return (w[i >> 2] >> ((i & 3u) * 8u)) & 0xffu;
+}
+
+/* shader/kd_bytes.comp:30-39: index of the first byte in which the two 16-byte strings differ, or 16 */
+static uint32_t kd_common_prefix(const uint32_t a[4], const uint32_t b[4]) {
+    for (uint32_t i = 0; i < 16u; i += 1) {
+        if (kd_byte_at(a, i) != kd_byte_at(b, i)) return i;
+    }
+    return 16u;
+}
+
+/* shader/kd_bytes.comp:70-72 */
+static uint32_t kd_pack_entry(uint32_t b, float p) {
+    return b | ((uint32_t)moe_ref_f2h(p) << 16);
+}
+
+/* shader/kd_bytes.comp:96-147.  The shader accumulates A and H with float atomics, i.e. in whatever
+ * order the 256 threads arrive; here tokens are added in ascending order.  The 256-way sum of a
+ * depth's byte masses follows the shader's halving tree (:55-68). */
+void moe_ref_kd_bytes(const float *logits, const uint32_t *toks, const uint32_t *cont, uint32_t *outp,
+                      uint32_t rows, uint32_t vocab) {
+    enum { D = 16, K = 8 };
+#pragma omp parallel for schedule(dynamic, 1)
+    for (uint32_t r = 0; r < rows; r += 1) {
+        const uint32_t *cw = cont + (size_t)r * 5u;
+        const uint32_t nd = cont[(size_t)r * 5u + 4u] < D ? cont[(size_t)r * 5u + 4u] : D; /* :100 */
+        uint32_t *o = outp + (size_t)r * D * K;
+        for (uint32_t i = nd * K; i < D * K; i += 1) o[i] = 0u; /* :101-103 */
+        float A[D + 1];
+        static _Thread_local float H[D][256];
+        memset(A, 0, sizeof(A));
+        memset(H, 0, sizeof(H));
+        const float *lg = logits + (size_t)r * vocab;
+        float m = -3.0e38f; /* :110 */
+        for (uint32_t t = 0; t < vocab; t += 1) m = lg[t] > m ? lg[t] : m;
+        for (uint32_t t = 0; t < vocab; t += 1) { /* :115-127 */
+            const uint32_t *tw = toks + (size_t)t * 5u;
+            const uint32_t len = tw[4];
+            if (len == 0u) continue;
+            const float e = expf(lg[t] - m);
+            const uint32_t lcp = kd_common_prefix(tw, cw);
+            uint32_t a = len < nd ? len : nd;
+            a = lcp < a ? lcp : a;
+            A[a] += e;
+            if (lcp < nd && lcp < len) H[lcp][kd_byte_at(tw, lcp)] += e;
+        }
+        for (uint32_t l = 0; l < nd; l += 1) { /* :129-146 */
+            float ztrue = 0.0f;
+            for (uint32_t k = l + 1u; k <= D; k += 1) ztrue += A[k];
+            float red[256], v[256];
+            memcpy(red, H[l], sizeof(red));
+            memcpy(v, H[l], sizeof(v));
+            for (uint32_t s = 128u; s > 0u; s >>= 1) {
+                for (uint32_t i = 0; i < s; i += 1) red[i] += red[i + s];
+            }
+            float total = ztrue + red[0];
+            total = total > 1e-30f ? total : 1e-30f;
+            o[l * K] = kd_pack_entry(kd_byte_at(cw, l), ztrue / total);
+            for (uint32_t j = 1; j < K; j += 1) {
+                uint32_t b = 0; /* :74-94: largest mass, lowest byte among equals */
+                for (uint32_t i = 1; i < 256u; i += 1) {
+                    if (v[i] > v[b]) b = i;
+                }
+                o[l * K + j] = kd_pack_entry(b, v[b] / total);
+                v[b] = -1.0f;
+            }
+        }
+    }
+}
+
 /* src/qwen.c:788-836 (mda_qwen_route_rec) then src/qwen.c:847-906
  * (mda_qwen_moe_rec from the first grouped product on). */
 int moe_ref_layer(moe_ref_layer_t *L) {

@@ -90,6 +90,15 @@ void moe_ref_residual_rmsnorm(const uint16_t *x16, const float *delta, uint16_t 
  * overflow to infinity), as the upload of a layer's weights does. */
 void moe_ref_bf16_to_f16(uint32_t *w, uint64_t n);
 
+/* shader/kd_bytes.comp:96-147 (call mda_teach_sink, src/teach.c:108-128): the teacher's next-token
+ * distribution over a byte-level vocabulary turned into per-byte distributions along the true
+ * continuation.  logits [rows x vocab] fp32; toks [vocab x 5] u32 (16 bytes little-endian in four
+ * words, then the length; length 0 = not a byte string); cont [rows x 5] (the 16 bytes that follow,
+ * then how many of them count); outp [rows x 16 x 8] entries byte | fp16(probability) << 16:
+ * entry 0 of depth l is the true byte, entries 1..7 the most probable other bytes. */
+void moe_ref_kd_bytes(const float *logits, const uint32_t *toks, const uint32_t *cont, uint32_t *outp,
+                      uint32_t rows, uint32_t vocab);
+
 /* One whole layer in the order of src/qwen.c:788-907 (mda_qwen_route_rec then
  * mda_qwen_moe_rec from the first grouped product on).  All buffers are
  * caller-owned; see moe_ref_layer_t. */

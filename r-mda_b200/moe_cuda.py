@@ -50,6 +50,10 @@ class PcBf16(C.Structure):
     _fields_ = [("n", C.c_uint32)]
 
 
+class PcKd(C.Structure):
+    _fields_ = [("rows", C.c_uint32), ("vocab", C.c_uint32)]
+
+
 class Layer(C.Structure):
     _fields_ = (
         [(n, C.c_uint32) for n in ("rows", "d", "experts", "topk", "inter", "shared", "pstride", "hc",
@@ -113,6 +117,7 @@ def lib() -> C.CDLL:
         L.moe_cuda_absmax.argtypes = [vp, vp, vp, PcSlot]
         L.moe_cuda_cast_f16.argtypes = [vp, vp, vp, vp, PcSlot]
         L.moe_cuda_bf16_to_f16.argtypes = [vp, vp, PcBf16]
+        L.moe_cuda_kd_bytes.argtypes = [vp, vp, vp, vp, vp, PcKd]
         L.moe_cuda_moe_rows.restype = u32
         L.moe_cuda_moe_rows.argtypes = [u32, u32, u32]
         L.moe_cuda_layer.argtypes = [vp, C.POINTER(Layer)]
@@ -266,6 +271,9 @@ class Ctx:
 
     def bf16_to_f16(self, w, n_words):
         lib().moe_cuda_bf16_to_f16(self.p, _ptr(w), PcBf16(n_words))
+
+    def kd_bytes(self, logits, toks, cont, outp, rows, vocab):
+        lib().moe_cuda_kd_bytes(self.p, _ptr(logits), _ptr(toks), _ptr(cont), _ptr(outp), PcKd(rows, vocab))
 
     def layer(self, **kw):
         L = Layer()

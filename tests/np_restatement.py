@@ -79,3 +79,31 @@ def layer(proj, x16, wgu, wdown, K, wsgu=None, wsdown=None, requantise=True):
         sg = 1.0 / (1.0 + np.exp(-proj[:, E].astype(np.float64)))
         out += sg[:, None] * sh
     return idx, wt, out
+
+
+def kd_bytes(logits, toks, cont):
+    """Per-byte teacher distributions along the true continuation, from the definition: at depth l,
+    among the tokens longer than l bytes that agree with the continuation on its first l bytes,
+    the probability that byte l is the true one, and the seven most probable other bytes.
+    Returns (byte u32 [rows, 16, 8], probability f64 [rows, 16, 8]); depths >= cont[:, 4] are zero."""
+    V = toks.shape[0]
+    tb = np.ascontiguousarray(toks[:, :4]).view(np.uint8).reshape(V, 16)      # little-endian bytes
+    length = toks[:, 4].astype(np.int64)
+    rows = logits.shape[0]
+    byte = np.zeros((rows, 16, 8), np.uint32)
+    prob = np.zeros((rows, 16, 8), np.float64)
+    for r in range(rows):
+        c = np.ascontiguousarray(cont[r, :4]).view(np.uint8)
+        nd = min(int(cont[r, 4]), 16)
+        lg = logits[r].astype(np.float64)
+        e = np.where(length > 0, np.exp(lg - lg.max()), 0.0)
+        agree = np.concatenate([np.ones((V, 1), bool), np.cumprod(tb == c, axis=1).astype(bool)], axis=1)  # [V, 17]
+        for l in range(nd):
+            alive = agree[:, l] & (length > l)
+            total = max(e[alive].sum(), 1e-30)
+            byte[r, l, 0], prob[r, l, 0] = c[l], e[alive & agree[:, l + 1]].sum() / total
+            other = alive & ~agree[:, l + 1]
+            mass = np.bincount(tb[other, l], weights=e[other], minlength=256)
+            top = np.argsort(-mass, kind="stable")[:7]                          # ties -> lower byte
+            byte[r, l, 1:], prob[r, l, 1:] = top, mass[top] / total
+    return byte, prob

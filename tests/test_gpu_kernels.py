@@ -221,6 +221,31 @@ def test_bf16_to_f16_in_place(ctx, oracle):
         assert np.array_equal(d.read(np.uint32, (n_words,)), oracle.bf16_to_f16(words))
 
 
+def test_kd_bytes(ctx, oracle):
+    """The distillation sink (shader/kd_bytes.comp): bytes as the oracle's wherever the masses are not
+    within rounding of one another, probabilities to fp16 accuracy; the shader itself sums in
+    arrival order, so bit-exactness is not defined for it."""
+    from tests.test_oracle import kd_inputs
+    for seed, rows, vocab in ((31, 24, 3000), (32, 5, 70001)):
+        logits, toks, cont = kd_inputs(seed, rows, vocab)
+        d_out = ctx.alloc(rows * 16 * 8 * 4)
+        d_out.fill(0xdeadbeef)
+        ctx.kd_bytes(ctx.upload(logits), ctx.upload(toks), ctx.upload(cont), d_out, rows, vocab)
+        ctx.flush()
+        got = d_out.read(np.uint32, (rows, 16, 8))
+        ref = oracle.kd_bytes(logits, toks, cont)
+        pg = (got >> 16).astype(np.uint16).view(np.float16).astype(np.float64)
+        pr = (ref >> 16).astype(np.uint16).view(np.float16).astype(np.float64)
+        assert np.all(np.abs(pg - pr) <= 1.5e-3 * pr + 1e-7)
+        differ = (got & 0xffff) != (ref & 0xffff)
+        # a different byte is only acceptable between two candidates of (nearly) the same mass
+        nxt = np.concatenate([pr[..., 1:], pr[..., -1:]], -1)
+        prv = np.concatenate([pr[..., :1], pr[..., :-1]], -1)
+        near = (np.abs(pr - nxt) <= 1.5e-3 * pr + 1e-7) | (np.abs(pr - prv) <= 1.5e-3 * pr + 1e-7)
+        assert not (differ & ~near).any() and not differ[..., 0].any()
+        assert differ.mean() < 0.01
+
+
 def test_fill_and_copy(ctx):
     b = ctx.alloc(4 * 1003)
     b.fill(0x12345678)

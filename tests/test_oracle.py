@@ -209,6 +209,41 @@ def test_bf16_to_f16(oracle):
     assert np.array_equal(got, want16)
 
 
+def kd_inputs(seed, rows=24, vocab=3000):
+    """A byte-level vocabulary (random strings of 1..16 bytes over a small alphabet so that prefixes
+    collide, plus a few entries of length 0) and continuations spelled from its tokens."""
+    rng = np.random.default_rng(seed)
+    tb = np.zeros((vocab, 16), np.uint8)
+    length = rng.integers(1, 17, vocab)
+    length[rng.choice(vocab, 20, replace=False)] = 0
+    for t in range(vocab):
+        tb[t, :length[t]] = rng.integers(97, 101, length[t])
+    toks = np.concatenate([tb.view(np.uint32).reshape(vocab, 4), length[:, None].astype(np.uint32)], axis=1)
+    cont = np.zeros((rows, 5), np.uint32)
+    for r in range(rows):
+        s = np.concatenate([tb[t, :length[t]] for t in rng.integers(0, vocab, 6)])[:16]
+        c = np.zeros(16, np.uint8)
+        c[:len(s)] = s
+        cont[r, :4] = c.view(np.uint32)
+        cont[r, 4] = [0, 1, 5, 16, 40][r % 5] if r < 10 else rng.integers(0, 17)
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    return logits, np.ascontiguousarray(toks), cont
+
+
+def test_kd_bytes_matches_numpy(oracle):
+    logits, toks, cont = kd_inputs(21)
+    got = oracle.kd_bytes(logits, toks, cont)
+    byte, prob = NP.kd_bytes(logits, toks, cont)
+    nd = np.minimum(cont[:, 4], 16)
+    for r in range(logits.shape[0]):
+        assert not got[r, nd[r]:].any()                                     # depths past the continuation stay zero
+    assert np.array_equal(got & 0xffff, byte)
+    p = (got >> 16).astype(np.uint16).view(np.float16).astype(np.float64)
+    assert np.all(np.abs(p - prob) <= 1e-3 * prob + 1e-7)                  # fp16 entries
+    live = np.arange(16)[None, :] < nd[:, None]
+    assert np.all(p[live].sum(-1) <= 1.0 + 2e-3) and np.all(p[live][:, 0] >= 0)
+
+
 def test_golden_vectors(oracle, synth):
     """The committed vectors were produced by tests/golden/make_golden.py from this oracle after
     it agreed with the numpy restatement; they catch any later drift of either."""
