@@ -185,6 +185,46 @@ def test_damaged_shards_are_refused(wlib, tmp_path):
     assert wlib.moe_st_open_set(str(tmp_path / "nowhere").encode()).n == 0
 
 
+def test_header_scanner_survives_mutations(wlib, tmp_path):
+    """Seeded byte mutations, insertions, deletions and truncations of a valid shard: the reader either
+    refuses the file or hands out tensors whose bytes lie inside the mapping."""
+    import random
+    rng = np.random.default_rng(6)
+    write_safetensors(tmp_path / "a.safetensors", layer_tensors(rng, 0, 32, 4, 32, 32), pretty=True, metadata={"k": "v"})
+    raw = (tmp_path / "a.safetensors").read_bytes()
+    hlen = struct.unpack("<Q", raw[:8])[0]
+    names = [(PREFIX + "layers.0.mlp." + n).encode() for n in ("gate.weight", "experts.gate_up_proj", "experts.down_proj")]
+    random.seed(1)
+    sub = tmp_path / "m"
+    sub.mkdir()
+    parsed = 0
+    for _ in range(400):
+        b = bytearray(raw)
+        for _ in range(random.randint(1, 4)):
+            pos, mode = random.randint(0, 8 + hlen - 1), random.random()
+            if mode < 0.5:
+                b[pos] = random.randint(0, 255)
+            elif mode < 0.7:
+                b[pos] = random.choice(b'{}[]",:\\ 0123456789')
+            elif mode < 0.85:
+                del b[pos]
+            else:
+                b.insert(pos, random.choice(b'{}[]",:\\ 9'))
+        if random.random() < 0.2:
+            b = b[:random.randint(0, len(b))]
+        (sub / "x.safetensors").write_bytes(bytes(b))
+        st = wlib.moe_st_open_set(str(sub).encode())
+        if st.n:
+            parsed += 1
+            for nm in names:
+                t = wlib.moe_st_find(C.byref(st), nm)
+                if t.ok:                                                    # first and last byte must be readable
+                    C.string_at(t.data, 1)
+                    C.string_at(t.data + t.rows * t.cols * 2 - 1, 1)
+            wlib.moe_st_free_set(C.byref(st))
+    assert 0 < parsed < 400
+
+
 @pytest.mark.gpu
 def test_bank_upload_converts_in_place(wlib, ctx, oracle, tmp_path):
     """Shards -> page-locked bank -> device, bf16 rewritten as fp16 (mda_qwen_upload, src/qwen.c:381-394)."""
