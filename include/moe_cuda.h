@@ -79,6 +79,16 @@ void *moe_cuda_stream(moe_cuda_ctx_t *c);
 /* Test hook for host-side failure injection: the n-th allocation from now
  * (1 = the next one) is refused as if the device were out of memory. */
 void moe_cuda_fail_alloc_after(moe_cuda_ctx_t *c, int n);
+/* Every device-side wait (a pipeline barrier inside the grouped products, a
+ * cross-GPU flag in the expert-parallel layer) gives up after this many
+ * nanoseconds, records MOE_ERR_TIMEOUT and lets its kernel return.  Default
+ * 2 000 000 000.  (The reference blocks in vkQueueWaitIdle without a bound,
+ * src/vkc.c:655-668.) */
+void moe_cuda_set_wait_ns(moe_cuda_ctx_t *c, uint64_t ns);
+/* Test hook: runs the cross-GPU flag barrier against a peer that never
+ * signals, so that the bounded wait runs out.  Afterwards (moe_cuda_flush) the
+ * status is MOE_ERR_TIMEOUT and later calls are refused; no fault, no hang. */
+void moe_cuda_wait_selftest(moe_cuda_ctx_t *c);
 
 /* ---- buffers: mda_vkc_alloc / alloc_cached / free / fill / copy / write /
  *      read / flush (src/vkc.h:80-97) ------------------------------------- */
@@ -197,7 +207,7 @@ typedef struct moe_cuda_layer_t {
 } moe_cuda_layer_t;
 #define MOE_LAYER_UNFUSED 1u /* run the reference's kernel sequence step by step (fp32 g, absmax rescale) */
 #define MOE_LAYER_YE_F32 2u  /* keep expert outputs fp32 between the down product and the combine */
-#define MOE_LAYER_CHUNKED 4u /* experimental: weight-stationary products over per-expert token chunks (MMA width rounded to 16) instead of the reference's 128-row tile schedule */
+#define MOE_LAYER_CHUNKED 4u /* weight-stationary products over per-expert token chunks (MMA width rounded to 16, tcgen05 cta_group::2 pairs) instead of the reference's 128-row tile schedule; measured on a par with the default at 256 tokens per expert, so opt-in */
 #define MOE_LAYER_NO_PAIR 8u /* with MOE_LAYER_CHUNKED: one CTA per tile instead of tcgen05 cta_group::2 pairs */
 #define MOE_LAYER_MATERIALIZE_XP 16u /* write the permuted activations xp to HBM as the reference does, instead of letting the gate_up product gather the rows of x16 itself */
 
@@ -235,7 +245,12 @@ int moe_cuda_ep_unique_id(void *out128);
 /* Rows of each rank's expert-contiguous buffers: sized for the worst case
  * (every token of every rank routed to this rank), so no token is ever dropped. */
 uint32_t moe_cuda_ep_rows(uint32_t world, uint32_t max_rows, uint32_t experts, uint32_t topk);
-/* Collective: joins the communicator, allocates and cross-maps the buffers. */
+/* Collective: joins the communicator, allocates and cross-maps the buffers.
+ * All ranks succeed or fail together once the communicator exists.
+ * moe_cuda_destroy of such a context is collective too: peers read and write
+ * this rank's buffers, so every rank runs one more bounded flag barrier before
+ * the memory is freed.  A context that has failed frees only what no peer can
+ * reach and leaves its peer-visible buffers to process exit. */
 void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, int rank, int world,
                       const moe_cuda_ep_cfg_t *cfg);
 /* Collective: one MoE layer.  L->rows = this rank's tokens, L->experts = global

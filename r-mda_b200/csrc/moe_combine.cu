@@ -40,7 +40,7 @@ moe_combine_kernel(moe_combine_args a) {
         __syncthreads();
         if (threadIdx.x < a.topk) {
             uint32_t g = a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank;
-            if (g < MOE_MAX_TOPK) atomicOr(&s_mask, 1u << g);
+            if (g < a.world) atomicOr(&s_mask, 1u << g);  // a row the router refused carries ~0: no term
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -53,10 +53,13 @@ moe_combine_kernel(moe_combine_args a) {
             s_terms = n;
         }
     } else if (threadIdx.x < a.topk) {
+        uint32_t sl = a.slot[(size_t)r * a.topk + threadIdx.x];
         if (PEER) {  // expert-parallel, one row per pair: read from the GPU that owns the expert, over NVLink
-            s_y[threadIdx.x] = reinterpret_cast<const YT *>(a.y_peers[a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank]);
+            const uint32_t g = a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank;
+            s_y[threadIdx.x] = reinterpret_cast<const YT *>(a.y_peers[g < a.world ? g : 0u]);
+            if (g >= a.world) sl = ~0u;
         }
-        s_slot[threadIdx.x] = a.slot[(size_t)r * a.topk + threadIdx.x];
+        s_slot[threadIdx.x] = sl;  // ~0: a pair the router refused, contributes nothing
         s_wt[threadIdx.x] = a.wt[(size_t)r * a.topk + threadIdx.x];
     }
     if (threadIdx.x >= 32 && threadIdx.x < 32 + a.hc && a.hc <= 7) {
@@ -76,6 +79,7 @@ moe_combine_kernel(moe_combine_args a) {
     for (uint32_t c = threadIdx.x * 4u; c < a.d; c += CB_THREADS * 4u, it += 1) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (uint32_t j = 0; j < terms; j += 1) {
+            if (s_slot[j] == ~0u) continue;
             float4 v = moe_load4((PEER ? s_y[j] : y) + (size_t)s_slot[j] * a.d + c);
             float w = s_wt[j];
             acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
@@ -152,7 +156,8 @@ void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a) {
     if (!MOE_LIVE(c)) return;
     MOE_REQUIRE(c, (a.y_peers != NULL && a.per_gpu) || (a.wt != NULL && a.slot != NULL && (a.y != NULL || a.y_peers != NULL)),
                 "combine: null buffer");
-    MOE_REQUIRE(c, a.y_peers == NULL || (a.idx != NULL && a.experts_per_rank >= 1), "combine: peer rows need idx");
+    MOE_REQUIRE(c, a.y_peers == NULL || (a.idx != NULL && a.experts_per_rank >= 1 && a.world >= 1 && a.world <= 16),
+                "combine: peer rows need idx and the world size");
     MOE_REQUIRE(c, a.h != NULL || a.y16 != NULL, "combine: no output");
     MOE_REQUIRE(c, a.sh == NULL || a.proj != NULL, "combine: shared term needs proj");
     MOE_REQUIRE(c, a.topk >= 1 && a.topk <= MOE_MAX_TOPK, "combine: topk %u outside 1..16", a.topk);

@@ -22,6 +22,7 @@ struct moe_tmap_entry {
     const void *ptr;
     uint64_t rows, cols;
     uint32_t box_rows, box_cols;
+    uint32_t kind;  // 0: plain 2-D; 1: gate/up interleaved 4-D
     CUtensorMap map;
 };
 
@@ -40,7 +41,7 @@ struct moe_cuda_ctx {
     uint32_t *dev_status_dev;
     void *scratch[MOE_SCR_COUNT];
     size_t scratch_bytes[MOE_SCR_COUNT];
-    moe_tmap_entry tmaps[32];
+    moe_tmap_entry tmaps[128];
     int n_tmaps, next_tmap;
     void *encode_tiled;  // cuTensorMapEncodeTiled, resolved at create
     bool prof;
@@ -52,6 +53,7 @@ struct moe_cuda_ctx {
     uint32_t *ticket;  // device word, zero between kernels: "last block done" counter
     bool sw_attr_set[8];
     moe_ep_state *ep;
+    uint64_t wait_ns;  // bound of every device-side wait (mbarriers, cross-GPU flags)
 };
 
 void moe_fail(moe_cuda_ctx *c, int code, const char *fmt, ...);
@@ -60,6 +62,10 @@ bool moe_poll_device_status(moe_cuda_ctx *c);
 void moe_ep_teardown(moe_cuda_ctx *c);
 const CUtensorMap *moe_tmap_2d_f16(moe_cuda_ctx *c, const void *ptr, uint64_t rows, uint64_t cols,
                                    uint32_t box_rows, uint32_t box_cols);
+
+// 4-D fp16 tensor map over an expert bank [experts][2][inter][k] (gate rows then up rows per expert) whose
+// box (64 k, 2, 64 inter, 1 expert) lands in shared memory as 128 rows: row 2i = gate row i, row 2i+1 = up row i.
+const CUtensorMap *moe_tmap_gate_up_f16(moe_cuda_ctx *c, const void *ptr, uint32_t experts, uint32_t inter, uint32_t k);
 
 #define MOE_LIVE(c) ((c) != NULL && (c)->status == MOE_OK)
 
@@ -121,10 +127,10 @@ void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void
                    uint32_t sa, uint32_t sb, uint32_t experts_in_B, uint32_t a_rows, bool prefix = false,
                    const uint32_t *src_row = NULL);
 
-// Weight-stationary grouped product over token chunks (moe_mm_swap.cu).
+// Weight-stationary grouped product over token chunks (moe_mm_ws.cu).
 void moe_launch_chunks(moe_cuda_ctx *c, const uint32_t *count, const uint32_t *off, uint32_t experts, void *chunks,
                        uint32_t *n_chunks, uint32_t max_chunks);
-void moe_launch_mm_swap(moe_cuda_ctx *c, int mode, int pair, const void *X, uint32_t rows_x, const void *W,
+void moe_launch_mm_ws(moe_cuda_ctx *c, int mode, int pair, const void *X, uint32_t rows_x, const void *W,
                         uint32_t experts_in_W, void *C, uint32_t ldc, const void *chunks, const uint32_t *n_chunks,
                         uint32_t max_chunks, uint32_t n, uint32_t k);
 
@@ -147,6 +153,7 @@ struct moe_combine_args {
     const uint32_t *idx;
     const void *const *y_peers;
     uint32_t experts_per_rank;
+    uint32_t world;      // number of GPUs behind y_peers
     uint32_t src_base;
     bool per_gpu;
 };

@@ -41,6 +41,7 @@ extern "C" moe_cuda_ctx_t *moe_cuda_create(int device, void *stream) {
     if (c == NULL) return NULL;
     c->device = device;
     c->status = MOE_OK;
+    c->wait_ns = 2000000000ull;
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) {
         moe_fail(c, MOE_ERR_CUDA, "no usable CUDA device %d: %s", device, cudaGetErrorString(e));
@@ -115,6 +116,10 @@ extern "C" void *moe_cuda_stream(moe_cuda_ctx_t *c) { return c == NULL ? NULL : 
 
 extern "C" void moe_cuda_fail_alloc_after(moe_cuda_ctx_t *c, int n) {
     if (c != NULL) c->fail_alloc_countdown = n;
+}
+
+extern "C" void moe_cuda_set_wait_ns(moe_cuda_ctx_t *c, uint64_t ns) {
+    if (c != NULL && ns != 0) c->wait_ns = ns;
 }
 
 extern "C" uint64_t moe_cuda_launches(moe_cuda_ctx_t *c) { return c == NULL ? 0 : c->launches; }
@@ -286,7 +291,7 @@ const CUtensorMap *moe_tmap_2d_f16(moe_cuda_ctx *c, const void *ptr, uint64_t ro
     if (!MOE_LIVE(c)) return NULL;
     for (int i = 0; i < c->n_tmaps; i += 1) {
         moe_tmap_entry *t = &c->tmaps[i];
-        if (t->ptr == ptr && t->rows == rows && t->cols == cols && t->box_rows == box_rows && t->box_cols == box_cols) {
+        if (t->kind == 0 && t->ptr == ptr && t->rows == rows && t->cols == cols && t->box_rows == box_rows && t->box_cols == box_cols) {
             return &t->map;
         }
     }
@@ -295,7 +300,7 @@ const CUtensorMap *moe_tmap_2d_f16(moe_cuda_ctx *c, const void *ptr, uint64_t ro
                  (unsigned long long)rows, (unsigned long long)cols);
         return NULL;
     }
-    int at = c->n_tmaps < 32 ? c->n_tmaps++ : (c->next_tmap++ & 31);
+    int at = c->n_tmaps < 128 ? c->n_tmaps++ : (c->next_tmap++ & 127);
     moe_tmap_entry *t = &c->tmaps[at];
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {cols * 2};
@@ -317,5 +322,39 @@ const CUtensorMap *moe_tmap_2d_f16(moe_cuda_ctx *c, const void *ptr, uint64_t ro
     t->cols = cols;
     t->box_rows = box_rows;
     t->box_cols = box_cols;
+    t->kind = 0;
+    return &t->map;
+}
+
+const CUtensorMap *moe_tmap_gate_up_f16(moe_cuda_ctx *c, const void *ptr, uint32_t experts, uint32_t inter, uint32_t k) {
+    if (!MOE_LIVE(c)) return NULL;
+    for (int i = 0; i < c->n_tmaps; i += 1) {
+        moe_tmap_entry *t = &c->tmaps[i];
+        if (t->kind == 1 && t->ptr == ptr && t->rows == experts && t->cols == k && t->box_rows == inter) return &t->map;
+    }
+    if (((uintptr_t)ptr & 15) != 0 || k % 8u != 0 || inter % 64u != 0 || experts == 0) {
+        moe_fail(c, MOE_ERR_ARG, "tensor map: gate/up bank %p experts %u inter %u k %u not TMA-addressable", ptr, experts, inter, k);
+        return NULL;
+    }
+    int at = c->n_tmaps < 128 ? c->n_tmaps++ : (c->next_tmap++ & 127);
+    moe_tmap_entry *t = &c->tmaps[at];
+    cuuint64_t dims[4] = {k, 2, inter, experts};
+    cuuint64_t strides[3] = {(cuuint64_t)inter * k * 2, (cuuint64_t)k * 2, (cuuint64_t)2 * inter * k * 2};
+    cuuint32_t box[4] = {64, 2, 64, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = ((moe_encode_fn)c->encode_tiled)(&t->map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, (void *)ptr, dims, strides, box,
+                                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        moe_fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled (gate/up bank) failed: %d", (int)r);
+        t->ptr = NULL;
+        return NULL;
+    }
+    t->ptr = ptr;
+    t->rows = experts;
+    t->cols = k;
+    t->box_rows = inter;
+    t->box_cols = 64;
+    t->kind = 1;
     return &t->map;
 }

@@ -84,7 +84,6 @@ static bool moe_nccl_load(char *why, size_t n) {
 
 #define MOE_EP_MAX_WORLD 16
 #define EP_FLAG_WORDS 128u  // 6 barrier sites (3 per micro-batch) x 16 ranks of epoch flags, padded
-#define EP_WAIT_NS 2000000000ull
 
 #define EP_MAX_MB 2  // micro-batches per layer call
 
@@ -149,10 +148,31 @@ extern "C" uint32_t moe_cuda_ep_rows(uint32_t world, uint32_t max_rows, uint32_t
     return rows < (1ull << 31) ? (uint32_t)rows : 0;
 }
 
+__global__ void moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t world, uint32_t rank, uint32_t site, uint32_t epoch,
+                                      uint32_t *status, uint64_t wait_ns);
+
+// Destroying an expert-parallel context is collective: peers write into and read
+// from this rank's xin / yout / sync buffers, so they must all have finished
+// their last layer before the memory goes away.  A healthy context runs one more
+// bounded flag barrier (its own site) first.  A failed context cannot know what
+// its peers still have in flight: it closes its mappings of their memory but
+// leaves its own exported buffers allocated until the process exits.
+#define EP_SITE_TEARDOWN 6u
 void moe_ep_teardown(moe_cuda_ctx *c) {
     if (c == NULL || c->ep == NULL) return;
     moe_ep_state *ep = c->ep;
-    if (c->stream != NULL) cudaStreamSynchronize(c->stream);
+    bool mapped = ep->sync_peer_dev != NULL && ep->sync != NULL;
+    for (int r = 0; r < ep->world && mapped; r += 1) mapped = ep->sync_peer[r] != NULL;
+    bool rendezvous = false;
+    if (c->stream != NULL && c->status == MOE_OK && mapped && ep->world > 1) {
+        ep->epoch += 1;
+        moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world, (uint32_t)ep->rank,
+                                                       EP_SITE_TEARDOWN, ep->epoch, c->dev_status_dev, c->wait_ns);
+        rendezvous = cudaStreamSynchronize(c->stream) == cudaSuccess && moe_poll_device_status(c);
+    } else if (c->stream != NULL) {
+        cudaStreamSynchronize(c->stream);
+        rendezvous = ep->world == 1 && c->status == MOE_OK;
+    }
     for (int r = 0; r < ep->world; r += 1) {
         if (r == ep->rank) continue;
         if (ep->xin_peer[r] != NULL) cudaIpcCloseMemHandle(ep->xin_peer[r]);
@@ -170,7 +190,8 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
         cudaEventDestroy(ep->ev_join);
     }
     for (size_t i = 0; i < sizeof(mine) / sizeof(mine[0]); i += 1) {
-        if (mine[i] != NULL) cudaFree(mine[i]);
+        const bool exported = mine[i] == (void *)ep->xin || mine[i] == (void *)ep->yout || mine[i] == (void *)ep->sync;
+        if (mine[i] != NULL && (rendezvous || !exported)) cudaFree(mine[i]);
     }
     if (ep->comm != NULL) {
         if (c->status == MOE_OK) g_nccl.CommDestroy(ep->comm);
@@ -180,11 +201,10 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
     c->ep = NULL;
 }
 
-__global__ void moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t world, uint32_t rank, uint32_t site, uint32_t epoch,
-                                      uint32_t *status);
 __global__ void moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch, uint32_t site,
                                    uint32_t table_off, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
-                                   uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status);
+                                   uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status,
+                                   uint64_t wait_ns);
 
 __global__ void moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xin_peers,
                                    uint32_t rows, uint32_t topk, uint32_t d8, uint32_t el, uint32_t world, uint32_t src_base);
@@ -267,6 +287,21 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     ep->slot = (uint32_t *)moe_cuda_alloc(c, R * K * 4);
     ep->wt = (float *)moe_cuda_alloc(c, R * K * 4);
     ep->bar = (uint32_t *)moe_cuda_alloc(c, 256);
+    {
+        // Every rank reaches this reduction whether or not its allocations succeeded, so that a rank
+        // that ran out of memory makes all ranks return an error together instead of leaving the
+        // others inside the handle exchange.
+        uint32_t *agree = NULL;
+        uint32_t flag[2] = {c->status == MOE_OK ? 0u : 1u, 0u};
+        bool ran = cudaMalloc((void **)&agree, 64) == cudaSuccess &&
+                   cudaMemcpyAsync(agree, flag, 8, cudaMemcpyHostToDevice, c->stream) == cudaSuccess &&
+                   g_nccl.AllReduce(agree, agree + 1, 1, ncclUint32, ncclSum, ep->comm, c->stream) == ncclSuccess &&
+                   cudaMemcpyAsync(flag, agree, 8, cudaMemcpyDeviceToHost, c->stream) == cudaSuccess &&
+                   cudaStreamSynchronize(c->stream) == cudaSuccess;
+        if (agree != NULL) cudaFree(agree);
+        if (!ran) moe_fail(c, MOE_ERR_COMM, "ep_init: the ranks could not agree on their set-up");
+        else if (flag[1] != 0) moe_fail(c, MOE_ERR_COMM, "ep_init: %u rank(s) failed to allocate their buffers", flag[1]);
+    }
     if (c->status != MOE_OK) return;
     if (nmb > 1) {
         // the transfer kernels of one slice must be able to run on SMs that hold a product CTA of the other
@@ -335,10 +370,11 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
 
 // Cross-GPU barrier without a library call: every rank stores the epoch into its
 // slot of every peer's flag row, then waits until all slots of its own row have
-// reached the epoch.  Flags only ever grow.  The wait is bounded (2 s): on
-// timeout the kernel records MOE_ERR_TIMEOUT and returns, it never hangs.
+// reached the epoch.  Flags only ever grow.  The wait is bounded (the context's
+// wait limit, 2 s unless moe_cuda_set_wait_ns changed it): on timeout the kernel
+// records MOE_ERR_TIMEOUT and returns, it never hangs.
 __device__ __forceinline__ void ep_signal_and_wait(uint32_t *const *sync_peers, uint32_t world, uint32_t rank, uint32_t site,
-                                                   uint32_t epoch, uint32_t *status) {
+                                                   uint32_t epoch, uint32_t *status, uint64_t wait_ns) {
     // called by threads 0..world-1 of a block after a __syncthreads(); thread p talks to rank p
     uint32_t p = threadIdx.x;
     if (p < world) {
@@ -356,7 +392,7 @@ __device__ __forceinline__ void ep_signal_and_wait(uint32_t *const *sync_peers, 
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
                 if (t0 == 0) {
                     t0 = now;
-                } else if (now - t0 > EP_WAIT_NS) {
+                } else if (now - t0 > wait_ns) {
                     atomicCAS(status, 0u, (uint32_t)MOE_ERR_TIMEOUT | ((20u + site) << 8));
                     break;
                 }
@@ -367,8 +403,27 @@ __device__ __forceinline__ void ep_signal_and_wait(uint32_t *const *sync_peers, 
 
 __global__ void __launch_bounds__(32)
 moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t world, uint32_t rank, uint32_t site, uint32_t epoch,
-                      uint32_t *status) {
-    ep_signal_and_wait(sync_peers, world, rank, site, epoch, status);
+                      uint32_t *status, uint64_t wait_ns) {
+    ep_signal_and_wait(sync_peers, world, rank, site, epoch, status, wait_ns);
+}
+
+// Runs the cross-GPU flag barrier as rank 0 of a two-rank group whose second
+// rank does not exist: both entries of the peer table point at one local,
+// zeroed flag buffer, so the flag of rank 1 is never set and the wait must run
+// into the context's limit, record MOE_ERR_TIMEOUT and return.  Nothing faults
+// and nothing hangs; the context is left failed (sticky), as after a real
+// timeout.
+extern "C" void moe_cuda_wait_selftest(moe_cuda_ctx_t *c) {
+    if (!MOE_LIVE(c)) return;
+    uint8_t *buf = (uint8_t *)moe_scratch(c, MOE_SCR_EP, 4096);
+    if (buf == NULL) return;
+    MOE_CUDA_TRY(c, cudaMemsetAsync(buf, 0, 4096, c->stream));
+    void *table[MOE_EP_MAX_WORLD] = {};
+    table[0] = buf;
+    table[1] = buf;
+    MOE_CUDA_TRY(c, cudaMemcpyAsync(buf + 2048, table, sizeof(table), cudaMemcpyHostToDevice, c->stream));
+    moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)(buf + 2048), 2u, 0u, 0u, 1u, c->dev_status_dev, c->wait_ns);
+    MOE_LAUNCHED(c);
 }
 
 // From all ranks' per-expert counts: where this rank's rows of expert e start in
@@ -380,7 +435,8 @@ moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t world, uint32_t rank
 __global__ void __launch_bounds__(512)
 moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch, uint32_t site,
                    uint32_t table_off, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
-                   uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status) {
+                   uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status,
+                   uint64_t wait_ns) {
     __shared__ uint32_t incl_s[512];
     uint32_t e = threadIdx.x;
     if (e < experts) {
@@ -388,7 +444,7 @@ moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_
         for (uint32_t p = 0; p < world; p += 1) sync_peers[p][table_off + rank * experts + e] = v;
     }
     __syncthreads();
-    ep_signal_and_wait(sync_peers, world, rank, site, epoch, status);
+    ep_signal_and_wait(sync_peers, world, rank, site, epoch, status, wait_ns);
     __syncthreads();
     const volatile uint32_t *cnt_all = sync_peers[rank] + table_off;
     uint32_t tot = 0, before = 0;
@@ -581,7 +637,7 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         // counts of every rank + plan (also orders this layer after every peer's previous combine)
         moe_ep_plan_kernel<<<1, 512, 0, c->stream>>>(count, (uint32_t *const *)ep->sync_peer_dev, ep->epoch, site,
                                                      EP_FLAG_WORDS + m * (uint32_t)ep->world * E, ep->dst_off[m], ep->tiles[m], E,
-                                                     (uint32_t)ep->world, (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev);
+                                                     (uint32_t)ep->world, (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev, c->wait_ns);
         c->launches += 1;
         if (m == 0) {
             if (L->off != NULL && nmb == 1) moe_cuda_copy(c, L->off, ep->dst_off[0], (size_t)E * 4);
@@ -612,7 +668,7 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         }
         if (m == 0 && nmb > 1) cudaEventRecord(ep->ev_disp, c->stream);
         moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
-                                                       (uint32_t)ep->rank, site + 1u, ep->epoch, c->dev_status_dev);  // all rows landed
+                                                       (uint32_t)ep->rank, site + 1u, ep->epoch, c->dev_status_dev, c->wait_ns);  // all rows landed
         c->launches += 1;
         if (m == 0) mark(3);
         moe_launch_mm(c, MOE_MM_SWIGLU_F16, xin_m, L->wgu, ep->hp16 + (size_t)m * mcap * I, NULL, ep->tiles[m], mcap, 2u * I, d,
@@ -629,7 +685,7 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         }
         if (m == 0) mark(5);
         moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
-                                                       (uint32_t)ep->rank, site + 2u, ep->epoch, c->dev_status_dev);  // all result rows written
+                                                       (uint32_t)ep->rank, site + 2u, ep->epoch, c->dev_status_dev, c->wait_ns);  // all result rows written
         c->launches += 1;
         if (m == 0) mark(6);
         if (rows != 0) {
@@ -655,6 +711,7 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             a.idx = idx + (size_t)row0 * K;
             a.y_peers = (const void *const *)ep->yout_peer_dev[m];
             a.experts_per_rank = ep->el;
+            a.world = (uint32_t)ep->world;
             a.src_base = (uint32_t)ep->rank * ep->cap;
             a.per_gpu = ep->per_gpu;
             moe_launch_combine(c, a);  // return all-to-all fused into the gather: one partial row per owning GPU

@@ -142,11 +142,11 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
         int pair2 = ((L->flags & MOE_LAYER_NO_PAIR) == 0 && d % 256u == 0) ? 2 : 1;
         if (d % 128u != 0) pair2 = 0;  // the down product needs whole 128-row weight tiles
         moe_launch_chunks(c, count, off, E, b.chunks, b.n_chunks, max_chunks);
-        moe_launch_mm_swap(c, MOE_MM_SWIGLU_F16, pair1, b.xp, M, L->wgu, E, b.hp16, I, b.chunks, b.n_chunks, max_chunks,
+        moe_launch_mm_ws(c, MOE_MM_SWIGLU_F16, pair1, b.xp, M, L->wgu, E, b.hp16, I, b.chunks, b.n_chunks, max_chunks,
                            2u * I, d);  // :847-877 in one kernel
         mark(c, 4);
         if (pair2 != 0) {
-            moe_launch_mm_swap(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, pair2, b.hp16, M, L->wdown, E, b.ye, d, b.chunks,
+            moe_launch_mm_ws(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, pair2, b.hp16, M, L->wdown, E, b.ye, d, b.chunks,
                                b.n_chunks, max_chunks, d, I);  // :878
         } else {
             moe_launch_mm(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, b.hp16, L->wdown, b.ye, NULL, tiles, M, d, I,

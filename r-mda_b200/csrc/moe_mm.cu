@@ -58,6 +58,7 @@ struct MmArgs {
     const __half *X;
     uint32_t ldx;
     uint32_t *status;
+    uint64_t wait_ns;
 };
 
 struct WorkItem {
@@ -139,7 +140,7 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     continue;
                 }
                 for (uint32_t kb = 0; kb < kblocks; kb += 1) {
-                    if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, 1)) {
+                    if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, 1, a.wait_ns)) {
                         ok = false;
                         break;
                     }
@@ -181,12 +182,12 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     continue;
                 }
                 uint32_t as = n_item & 1u, aph = (n_item >> 1) & 1u;
-                if (!mbar_wait(smem_u32(&bars->tmem_empty[as]), aph ^ 1u, abort, a.status, 2)) break;
+                if (!mbar_wait(smem_u32(&bars->tmem_empty[as]), aph ^ 1u, abort, a.status, 2, a.wait_ns)) break;
                 tc_fence_after();
                 uint32_t tmem_d = tmem_base + as * BN;
                 uint32_t idesc = umma_idesc(BM, it.nvalid);
                 for (uint32_t kb = 0; kb < kblocks; kb += 1) {
-                    if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort, a.status, 3)) {
+                    if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort, a.status, 3, a.wait_ns)) {
                         ok = false;
                         break;
                     }
@@ -241,7 +242,7 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             }
             for (uint32_t kb = 0; kb < kblocks; kb += 1) {
                 uint32_t got = 1;
-                if (lane == 0) got = mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, 5) ? 1u : 0u;
+                if (lane == 0) got = mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, 5, a.wait_ns) ? 1u : 0u;
                 got = __shfl_sync(0xffffffffu, got, 0);
                 if (!got) {
                     ok = false;
@@ -279,7 +280,7 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 continue;
             }
             uint32_t as = n_item & 1u, aph = (n_item >> 1) & 1u;
-            if (!mbar_wait(smem_u32(&bars->tmem_full[as]), aph, abort, a.status, 4)) break;
+            if (!mbar_wait(smem_u32(&bars->tmem_full[as]), aph, abort, a.status, 4, a.wait_ns)) break;
             tc_fence_after();
             uint32_t taddr = tmem_base + as * BN + ((q * 32u) << 16);
             size_t row = (size_t)it.mt * BM + q * 32u + lane;
@@ -392,6 +393,7 @@ void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void
     a.X = (const __half *)A;
     a.ldx = k;
     a.status = c->dev_status_dev;
+    a.wait_ns = c->wait_ns;
     uint32_t nt = mode == MOE_MM_SWIGLU_F16 ? n / BN : (n + BN - 1) / BN;
     uint64_t total = (uint64_t)(m / BM) * nt;
     uint32_t grid = total < (uint64_t)c->sm_count ? (uint32_t)total : (uint32_t)c->sm_count;

@@ -95,8 +95,15 @@ moe_route_kernel(const float *__restrict__ proj, uint32_t *__restrict__ idx, flo
             }
         }
         if (bad) {
+            // the shader would index count[~0u] here; refuse instead.  The row's entries are written as
+            // "no expert, weight 0" so that kernels already queued behind this one (place, send, combine)
+            // skip it instead of acting on values a previous call left there.
             if (lane == 0) atomicCAS(status, 0u, (uint32_t)MOE_ERR_ROUTE | (r << 8));
-            continue;  // the shader would index count[~0u] here; refuse instead
+            if (lane < topk) {
+                idx[(size_t)r * topk + lane] = ~0u;
+                wt[(size_t)r * topk + lane] = 0.0f;
+            }
+            continue;
         }
         // :52-60: z accumulated k = 0..topk-1 in fp32, then each weight
         float t = lane < topk ? expf(my_v - v0) : 0.0f;

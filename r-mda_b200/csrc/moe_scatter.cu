@@ -86,7 +86,9 @@ moe_scatter_colscan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ f
             run += v;
         }
         if (seg == 31) {
-            if (fill != NULL) fill[e] += run;          // state after the shader's atomics (:25)
+            // state after the shader's atomics (:25).  Only experts that occur are touched, as in the
+            // shader: moe_cuda_scatter scans up to the reference's 512 experts, the caller's fill[] may be shorter.
+            if (fill != NULL && run != 0) fill[e] += run;
             if (count_out != NULL) count_out[e] = run;  // per-expert totals double as the router's counts
         }
     }
@@ -149,6 +151,7 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
             }
         } else {
             s_slot[threadIdx.x] = ~0u;
+            slot[p0 + threadIdx.x] = ~0u;  // a pair the router refused: the combine skips it
         }
     }
     if (src_row != NULL || src_row_peers != NULL) return;

@@ -7,8 +7,6 @@
 
 namespace moe_tc {
 
-constexpr uint64_t WAIT_NS = 2000000000ull;  // bound of any single wait
-
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -37,8 +35,9 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 // Bounded wait.  False = gave up (own timeout, or another role raised abort).
+// wait_ns bounds any single wait (the context's limit, 2 s by default).
 static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort, uint32_t *status,
-                                       uint32_t site) {
+                                       uint32_t site, uint64_t wait_ns) {
     uint32_t spins = 0;
     uint64_t t0 = 0;
     while (!mbar_try_wait(bar, parity)) {
@@ -48,7 +47,7 @@ static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, vol
             uint64_t now = globaltimer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > WAIT_NS) {
+            } else if (now - t0 > wait_ns) {
                 *abort = 1;
                 atomicCAS(status, 0u, (uint32_t)MOE_ERR_TIMEOUT | (site << 8));
                 return false;

@@ -95,6 +95,8 @@ def lib() -> C.CDLL:
         L.moe_cuda_stream.restype = vp
         L.moe_cuda_stream.argtypes = [vp]
         L.moe_cuda_fail_alloc_after.argtypes = [vp, C.c_int]
+        L.moe_cuda_set_wait_ns.argtypes = [vp, C.c_uint64]
+        L.moe_cuda_wait_selftest.argtypes = [vp]
         L.moe_cuda_alloc.restype = vp
         L.moe_cuda_alloc.argtypes = [vp, sz]
         L.moe_cuda_alloc_pinned.restype = vp

@@ -28,6 +28,20 @@ def test_push_constant_layouts(mc):
     assert ctypes.sizeof(mc.PcElem) == 28 and ctypes.sizeof(mc.PcSlot) == 8
 
 
+def test_header_shares_the_reference_structs(tmp_path):
+    """tests/abi_pc_check.c includes the reference's unmodified src/pc.h before include/moe_cuda.h and
+    _Static_asserts sizes and offsets of src/pc.h:369-404; it must compile as C17 without a warning."""
+    import subprocess
+    import pytest
+    ref_src = os.environ.get("MOE_REFERENCE_SRC", "/root/reference/src")
+    if not os.path.exists(os.path.join(ref_src, "pc.h")):
+        pytest.skip("the reference tree is not mounted on this machine")
+    obj = tmp_path / "abi_pc_check.o"
+    r = subprocess.run(["gcc", "-std=gnu17", "-Wall", "-Wextra", "-Werror", "-c", "-I", ref_src, "-I", os.path.join(ROOT, "include"),
+                        os.path.join(ROOT, "tests", "abi_pc_check.c"), "-o", str(obj)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_no_cpu_fallback_without_device(mc):
     import torch
     if torch.cuda.is_available():

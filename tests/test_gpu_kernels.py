@@ -124,6 +124,27 @@ def test_scatter(ctx, oracle, mc, rows, E, K, d):
     assert np.array_equal(d_slot.read(np.uint32, (rows, K)), rslot)
 
 
+def test_scatter_leaves_words_after_fill_alone(ctx, oracle):
+    """moe_cuda_scatter has no expert count (src/pc.h:381-385) and scans the reference's 512 experts; like the
+    shader's atomics it must only touch fill[e] of experts that occur in idx.  fill is E words long
+    (src/qwen.c:171); the words behind it are canaries here."""
+    rows, E, K, d = 300, 8, 2, 64
+    rng = np.random.default_rng(5)
+    idx, _, count = oracle.route(rand_logits(rng, rows, E, E), E, K)
+    M = oracle.moe_rows(rows, K, E)
+    off, _ = oracle.scan(count, 128, M // 128)
+    x16 = rng.integers(0, 0x7bff, (rows, d)).astype(np.uint16)
+    fill0 = np.full(E + 504, 0xabcd1234, np.uint32)
+    fill0[:E] = 0
+    d_fill = ctx.upload(fill0)
+    d_xp, d_slot = ctx.zeros(M * d * 2), ctx.alloc(rows * K * 4)
+    ctx.scatter(ctx.upload(idx), ctx.upload(off), d_fill, ctx.upload(x16), d_xp, d_slot, rows, K, d // 8)
+    ctx.flush()
+    fill = d_fill.read(np.uint32, (E + 504,))
+    assert np.array_equal(fill[:E], count)
+    assert np.all(fill[E:] == 0xabcd1234)
+
+
 def _f16(rng, shape, std):
     return (rng.standard_normal(shape).astype(np.float32) * std).astype(np.float16).view(np.uint16)
 
@@ -266,6 +287,29 @@ def test_bad_shapes_set_sticky_status(mc):
         b = c.alloc(1 << 16)
         c.mm(b, b, b, None, b, 100, 128, 64)  # m not a multiple of 128
         assert c.status() == mc.MOE_ERR_ARG
+
+
+def test_bounded_wait_runs_out_and_reports(mc):
+    """A cross-GPU flag wait whose peer never signals: the kernel gives up after the context's
+    limit, returns, and the host reads MOE_ERR_TIMEOUT with the site of the wait.  Nothing
+    faults or hangs; the context stays refused afterwards (sticky)."""
+    import time
+    with mc.Ctx(0) as c:
+        c.check()
+        mc.lib().moe_cuda_set_wait_ns(c.p, 20_000_000)   # 20 ms
+        t0 = time.perf_counter()
+        mc.lib().moe_cuda_wait_selftest(c.p)
+        with pytest.raises(mc.MoeCudaError) as e:
+            c.flush()
+        assert time.perf_counter() - t0 < 1.5
+        assert e.value.code == mc.MOE_ERR_TIMEOUT
+        assert "site 20" in c.last_error()
+        assert mc.lib().moe_cuda_alloc(c.p, 64) is None  # later calls are no-ops
+    with mc.Ctx(0) as c:                                 # the device is still usable
+        c.check()
+        b = c.zeros(64)
+        c.flush()
+        assert np.all(b.read(np.uint32, (16,)) == 0)
 
 
 def test_alloc_refusal_is_sticky(mc):

@@ -80,6 +80,45 @@ def test_decode_sweep(ctx, mc, synth, oracle, T):
     check(run_layer(ctx, mc, cfg, inp, 0), ref)
 
 
+def test_refused_row_is_skipped_by_the_queued_kernels(ctx, mc, synth, oracle):
+    """A row of NaN logits cannot be routed.  The layer call fails with MOE_ERR_ROUTE, and the
+    kernels already queued behind the router act on "no expert, weight 0" for that row -- not on
+    what the previous call left in idx/wt -- so every other row still gets its exact result."""
+    import dataclasses
+    cfg = dataclasses.replace(synth.CONFIGS["c0"], T=256, name="c0-T256")
+    inp = synth.layer_inputs(cfg, 2)
+    ref = oracle.layer(inp.proj, inp.x16, inp.wgu, inp.wdown, cfg.K)
+    T, K, E = cfg.T, cfg.K, cfg.E
+    proj = inp.proj.copy()
+    bad = 37
+    proj[bad, :E] = np.nan
+    d = dict(x16=ctx.upload(inp.x16), wgu=ctx.upload(inp.wgu), wdown=ctx.upload(inp.wdown))
+    d_h = ctx.zeros(T * cfg.d * 4)
+    d_idx = ctx.alloc(T * K * 4).fill(3)          # stale values a previous call could have left
+    d_slot = ctx.alloc(T * K * 4).fill(5)
+    d_wt = ctx.alloc(T * K * 4).fill(0x3f800000)
+    ctx.layer(rows=T, d=cfg.d, experts=E, topk=K, inter=cfg.I, shared=0, pstride=cfg.pstride, hc=1, proj=ctx.upload(proj),
+              h=d_h, idx=d_idx, slot=d_slot, wt=d_wt, **d)
+    with pytest.raises(mc.MoeCudaError) as e:
+        ctx.flush()
+    assert e.value.code == mc.MOE_ERR_ROUTE
+    out = {}
+    with mc.Ctx(0) as reader:   # the failed context refuses every call; a second one reads its buffers
+        for name, buf, dt, shape in (("idx", d_idx, np.uint32, (T, K)), ("slot", d_slot, np.uint32, (T, K)),
+                                     ("wt", d_wt, np.float32, (T, K)), ("h", d_h, np.float32, (T, cfg.d))):
+            a = np.empty(shape, dt)
+            mc.lib().moe_cuda_read(reader.p, a.ctypes.data, buf.ptr, a.nbytes)
+            reader.check()
+            out[name] = a
+    assert np.all(out["idx"][bad] == 0xffffffff) and np.all(out["slot"][bad] == 0xffffffff) and np.all(out["wt"][bad] == 0)
+    assert np.all(out["h"][bad] == 0)
+    # the other rows: same experts; their outputs are within tolerance of a reference computed without the bad row's pairs
+    keep = np.arange(T) != bad
+    assert np.array_equal(out["idx"][keep], ref.idx[keep])
+    err = np.abs(out["h"][keep] - ref.h[keep, 0])
+    assert np.all(err <= ATOL_OUT + RTOL_OUT * np.abs(ref.h[keep, 0]))
+
+
 def test_shared_expert_small(ctx, mc, synth, oracle):
     import dataclasses
     cfg = dataclasses.replace(synth.CONFIGS["c2"], T=300, E=64, name="c2-small")

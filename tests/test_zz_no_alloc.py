@@ -42,6 +42,28 @@ def test_noalloc_scatter_equals_scatter_twice(ctx, oracle):
         assert np.array_equal(out["noalloc"][0], rslot)
 
 
+def test_noalloc_scatter_leaves_device_memory_as_it_found_it(ctx, oracle):
+    """What the name promises: once the first call on the device has looked up the table's
+    address, a call changes nothing in the amount of device memory in use (cudaMemGetInfo, read
+    through torch)."""
+    import torch
+    rng = np.random.default_rng(12)
+    rows, E, K, d = 2048, 128, 8, 128
+    idx, off, x16, M = _case(oracle, rng, rows, E, K, d)
+    d_idx, d_off, d_x = ctx.upload(idx), ctx.upload(off), ctx.upload(x16)
+    d_fill, d_xp, d_slot = ctx.zeros(E * 4), ctx.zeros(M * d * 2), ctx.alloc(rows * K * 4)
+    ctx.scatter_noalloc(d_idx, d_off, d_fill, d_x, d_xp, d_slot, rows, K, d // 8, E)   # first call: address look-up
+    ctx.flush()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(0)
+    for _ in range(3):
+        d_fill.fill(0)
+        ctx.scatter_noalloc(d_idx, d_off, d_fill, d_x, d_xp, d_slot, rows, K, d // 8, E)
+    ctx.flush()
+    free1, _ = torch.cuda.mem_get_info(0)
+    assert free1 == free0, f"device memory in use changed by {free0 - free1} bytes across moe_cuda_scatter_noalloc"
+
+
 def test_noalloc_scatter_refuses_oversize(mc):
     with mc.Ctx(0) as c:
         c.check()
