@@ -233,8 +233,9 @@ void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
 typedef struct moe_cuda_ep_cfg_t {
     uint32_t experts, topk, d, inter; /* global expert count; experts % world == 0, inter % 128 == 0 */
     uint32_t max_rows;                /* most tokens any rank will pass in one call */
-    uint32_t micro_batches;           /* 1 or 2 slices of the local tokens that pipeline NVLink transfers against
-                                         the products; 0 = automatic (2 with per-pair transfers over 4 or more ranks, else 1) */
+    uint32_t micro_batches;           /* 1 to 4 slices of the local tokens (equal parts rounded up to 8 rows) that pipeline
+                                         NVLink transfers against the products, each on its own stream;
+                                         0 = automatic (2 with per-pair transfers over 4 or more ranks, else 1) */
     uint32_t transfer;                /* MOE_EP_TRANSFER_*: what crosses NVLink */
 } moe_cuda_ep_cfg_t;
 #define MOE_EP_TRANSFER_AUTO 0u     /* PER_GPU up to 4 ranks, PER_PAIR beyond (measured crossover on B200) */
@@ -256,14 +257,19 @@ void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, int rank, int
 /* Collective: one MoE layer.  L->rows = this rank's tokens, L->experts = global
  * expert count, L->wgu / L->wdown = this rank's experts only.  L->slot receives
  * row numbers inside the owning rank's buffer (of the token's micro-batch),
- * L->off (one micro-batch only) this rank's first row per expert there.  Shared
- * expert, L->tiles and the flags are not supported. */
+ * L->off (one micro-batch only) this rank's first row per expert there.  The
+ * shared expert (L->shared, L->wsgu, L->wsdown: replicated weights) runs on
+ * every rank's own tokens and enters the combine as in the single-GPU layer
+ * (src/qwen.c:879-886, shader/moe_combine.comp:35).  L->tiles and the flags
+ * are not supported. */
 void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L);
 
 /* Per-stage device times of the last moe_cuda_layer call, in milliseconds, in
  * the order route, scan, scatter, gate_up, down, shared, combine (for
- * moe_cuda_ep_layer: router, counts + plan, dispatch + barrier, gate_up, down,
- * barrier, combine + return, of the first token slice) (after
+ * moe_cuda_ep_layer: router, counts + plan, dispatch + barrier (+ the shared
+ * expert), gate_up, down, barrier, combine + return; with several token slices
+ * each stage is the sum of the slices' times, every slice timed on its own
+ * stream) (after
  * mda_vkc_prof_begin / prof_report, src/vkc.c:595-653).  Enabled with
  * moe_cuda_prof(c, 1); reading them synchronises the stream. */
 #define MOE_PROF_STAGES 7

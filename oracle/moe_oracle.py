@@ -56,6 +56,14 @@ def threads() -> int:
     return int(lib().moe_ref_threads())
 
 
+def use_all_cores() -> int:
+    """Give the oracle every core this process may run on, whatever OMP_NUM_THREADS says
+    (torch.distributed.run sets it to 1 for its children).  Returns the thread count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().moe_ref_set_threads(C.c_int(n))
+    return threads()
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

@@ -41,6 +41,16 @@ int moe_ref_threads(void) {
 #endif
 }
 
+/* Launchers such as torch.distributed.run export OMP_NUM_THREADS=1 to their
+ * children; the timed CPU baseline asks for the machine's cores explicitly. */
+void moe_ref_set_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* shader/moe_route.comp:20-62.  The shader gives each of 32 lanes 16 candidate
  * columns and reduces (max value, then min index among the lanes holding it);
  * within a lane the scan keeps the first of equal values (strict >, :34).  The

@@ -32,6 +32,7 @@ float moe_ref_h2f(uint16_t h);
 uint16_t moe_ref_f2h(float f);
 
 int moe_ref_threads(void);
+void moe_ref_set_threads(int n);
 
 /* shader/moe_route.comp:20-62.  Returns 0, or -1 if some row has fewer than
  * topk selectable candidates (logit > -3.0e38 and not NaN): the shader would

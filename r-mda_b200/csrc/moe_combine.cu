@@ -30,115 +30,119 @@ moe_combine_kernel(moe_combine_args a) {
     __shared__ float s_red[CB_THREADS / 32];
     __shared__ const YT *s_y[PEER ? MOE_MAX_TOPK : 1];
     __shared__ uint32_t s_mask, s_terms;
-    uint32_t r = blockIdx.x;
     const YT *y = reinterpret_cast<const YT *>(a.y);
-    if (PEER && a.per_gpu) {
-        // Expert-parallel, one row per owning GPU: every GPU that owns some of the token's experts has
-        // already summed wt * row over those experts (moe_ep_partial_kernel); one such partial row per
-        // GPU comes over NVLink and the partial rows are added in ascending GPU order.
-        if (threadIdx.x == 0) s_mask = 0;
-        __syncthreads();
-        if (threadIdx.x < a.topk) {
-            uint32_t g = a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank;
-            if (g < a.world) atomicOr(&s_mask, 1u << g);  // a row the router refused carries ~0: no term
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            uint32_t n = 0;
-            for (uint32_t mk = s_mask; mk != 0; mk &= mk - 1u, n += 1) {
-                s_y[n] = reinterpret_cast<const YT *>(a.y_peers[__ffs((int)mk) - 1]);
-                s_slot[n] = a.src_base + r;
-                s_wt[n] = 1.0f;
+    // One row per block and pass; the expert-parallel layer launches a bounded grid (rows blockIdx.x,
+    // blockIdx.x + gridDim.x, ...) so that the peer loads can share the SMs with a grouped-product CTA.
+    for (uint32_t r = blockIdx.x; r < a.rows; r += gridDim.x) {
+        if (PEER && a.per_gpu) {
+            // Expert-parallel, one row per owning GPU: every GPU that owns some of the token's experts has
+            // already summed wt * row over those experts (moe_ep_partial_kernel); one such partial row per
+            // GPU comes over NVLink and the partial rows are added in ascending GPU order.
+            if (threadIdx.x == 0) s_mask = 0;
+            __syncthreads();
+            if (threadIdx.x < a.topk) {
+                uint32_t g = a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank;
+                if (g < a.world) atomicOr(&s_mask, 1u << g);  // a row the router refused carries ~0: no term
             }
-            s_terms = n;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                uint32_t n = 0;
+                for (uint32_t mk = s_mask; mk != 0; mk &= mk - 1u, n += 1) {
+                    s_y[n] = reinterpret_cast<const YT *>(a.y_peers[__ffs((int)mk) - 1]);
+                    s_slot[n] = a.src_base + r;
+                    s_wt[n] = 1.0f;
+                }
+                s_terms = n;
+            }
+        } else if (threadIdx.x < a.topk) {
+            uint32_t sl = a.slot[(size_t)r * a.topk + threadIdx.x];
+            if (PEER) {  // expert-parallel, one row per pair: read from the GPU that owns the expert, over NVLink
+                const uint32_t g = a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank;
+                s_y[threadIdx.x] = reinterpret_cast<const YT *>(a.y_peers[g < a.world ? g : 0u]);
+                if (g >= a.world) sl = ~0u;
+            }
+            s_slot[threadIdx.x] = sl;  // ~0: a pair the router refused, contributes nothing
+            s_wt[threadIdx.x] = a.wt[(size_t)r * a.topk + threadIdx.x];
         }
-    } else if (threadIdx.x < a.topk) {
-        uint32_t sl = a.slot[(size_t)r * a.topk + threadIdx.x];
-        if (PEER) {  // expert-parallel, one row per pair: read from the GPU that owns the expert, over NVLink
-            const uint32_t g = a.idx[(size_t)r * a.topk + threadIdx.x] / a.experts_per_rank;
-            s_y[threadIdx.x] = reinterpret_cast<const YT *>(a.y_peers[g < a.world ? g : 0u]);
-            if (g >= a.world) sl = ~0u;
+        if (threadIdx.x >= 32 && threadIdx.x < 32 + a.hc && a.hc <= 7) {
+            uint32_t s = threadIdx.x - 32;
+            float iv = a.inj != NULL ? a.inj[(size_t)r * a.inj_stride + a.inj_off + s] : 0.0f;
+            s_f[s] = moe_sigmoid(iv / (float)a.hc);  // :37
         }
-        s_slot[threadIdx.x] = sl;  // ~0: a pair the router refused, contributes nothing
-        s_wt[threadIdx.x] = a.wt[(size_t)r * a.topk + threadIdx.x];
-    }
-    if (threadIdx.x >= 32 && threadIdx.x < 32 + a.hc && a.hc <= 7) {
-        uint32_t s = threadIdx.x - 32;
-        float iv = a.inj != NULL ? a.inj[(size_t)r * a.inj_stride + a.inj_off + s] : 0.0f;
-        s_f[s] = moe_sigmoid(iv / (float)a.hc);  // :37
-    }
-    if (threadIdx.x == 64) {
-        s_f[7] = a.sh != NULL ? moe_sigmoid(a.proj[(size_t)r * a.pstride + a.sg_off]) : 0.0f;  // :35
-    }
-    __syncthreads();
-    const uint32_t terms = (PEER && a.per_gpu) ? s_terms : a.topk;
-    float sg = s_f[7];
-    float4 keep[NORM ? CB_MAXV : 1];
-    float ss = 0.0f;
-    uint32_t it = 0;
-    for (uint32_t c = threadIdx.x * 4u; c < a.d; c += CB_THREADS * 4u, it += 1) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t j = 0; j < terms; j += 1) {
-            if (s_slot[j] == ~0u) continue;
-            float4 v = moe_load4((PEER ? s_y[j] : y) + (size_t)s_slot[j] * a.d + c);
-            float w = s_wt[j];
-            acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
-            acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
-            acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
-            acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
+        if (threadIdx.x == 64) {
+            s_f[7] = a.sh != NULL ? moe_sigmoid(a.proj[(size_t)r * a.pstride + a.sg_off]) : 0.0f;  // :35
         }
-        if (a.sh != NULL) {
-            float4 v = moe_load4(a.sh + (size_t)r * a.d + c);
-            acc.x = __fadd_rn(acc.x, __fmul_rn(sg, v.x));
-            acc.y = __fadd_rn(acc.y, __fmul_rn(sg, v.y));
-            acc.z = __fadd_rn(acc.z, __fmul_rn(sg, v.z));
-            acc.w = __fadd_rn(acc.w, __fmul_rn(sg, v.w));
+        __syncthreads();
+        const uint32_t terms = (PEER && a.per_gpu) ? s_terms : a.topk;
+        float sg = s_f[7];
+        float4 keep[NORM ? CB_MAXV : 1];
+        float ss = 0.0f;
+        uint32_t it = 0;
+        for (uint32_t c = threadIdx.x * 4u; c < a.d; c += CB_THREADS * 4u, it += 1) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t j = 0; j < terms; j += 1) {
+                if (s_slot[j] == ~0u) continue;
+                float4 v = moe_load4((PEER ? s_y[j] : y) + (size_t)s_slot[j] * a.d + c);
+                float w = s_wt[j];
+                acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
+            }
+            if (a.sh != NULL) {
+                float4 v = moe_load4(a.sh + (size_t)r * a.d + c);
+                acc.x = __fadd_rn(acc.x, __fmul_rn(sg, v.x));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(sg, v.y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(sg, v.z));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(sg, v.w));
+            }
+            if (NORM) {
+                float4 xv = moe_load4(a.x16 + (size_t)r * a.d + c);
+                float f = s_f[0];
+                float4 v;
+                v.x = __fadd_rn(xv.x, __fmul_rn(__fmul_rn(acc.x, 2.0f), f));
+                v.y = __fadd_rn(xv.y, __fmul_rn(__fmul_rn(acc.y, 2.0f), f));
+                v.z = __fadd_rn(xv.z, __fmul_rn(__fmul_rn(acc.z, 2.0f), f));
+                v.w = __fadd_rn(xv.w, __fmul_rn(__fmul_rn(acc.w, 2.0f), f));
+                keep[it] = v;
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            if (a.h != NULL) {
+                for (uint32_t s = 0; s < a.hc; s += 1) {  // :36-38
+                    float f = a.hc <= 7 ? s_f[s]
+                                        : moe_sigmoid((a.inj != NULL ? a.inj[(size_t)r * a.inj_stride + a.inj_off + s] : 0.0f) / (float)a.hc);
+                    float4 *hp = reinterpret_cast<float4 *>(a.h + ((size_t)r * a.hc + s) * a.d + c);
+                    float4 hv = *hp;
+                    hv.x = __fadd_rn(hv.x, __fmul_rn(__fmul_rn(acc.x, 2.0f), f));
+                    hv.y = __fadd_rn(hv.y, __fmul_rn(__fmul_rn(acc.y, 2.0f), f));
+                    hv.z = __fadd_rn(hv.z, __fmul_rn(__fmul_rn(acc.z, 2.0f), f));
+                    hv.w = __fadd_rn(hv.w, __fmul_rn(__fmul_rn(acc.w, 2.0f), f));
+                    *hp = hv;
+                }
+            }
         }
         if (NORM) {
-            float4 xv = moe_load4(a.x16 + (size_t)r * a.d + c);
-            float f = s_f[0];
-            float4 v;
-            v.x = __fadd_rn(xv.x, __fmul_rn(__fmul_rn(acc.x, 2.0f), f));
-            v.y = __fadd_rn(xv.y, __fmul_rn(__fmul_rn(acc.y, 2.0f), f));
-            v.z = __fadd_rn(xv.z, __fmul_rn(__fmul_rn(acc.z, 2.0f), f));
-            v.w = __fadd_rn(xv.w, __fmul_rn(__fmul_rn(acc.w, 2.0f), f));
-            keep[it] = v;
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-        if (a.h != NULL) {
-            for (uint32_t s = 0; s < a.hc; s += 1) {  // :36-38
-                float f = a.hc <= 7 ? s_f[s]
-                                    : moe_sigmoid((a.inj != NULL ? a.inj[(size_t)r * a.inj_stride + a.inj_off + s] : 0.0f) / (float)a.hc);
-                float4 *hp = reinterpret_cast<float4 *>(a.h + ((size_t)r * a.hc + s) * a.d + c);
-                float4 hv = *hp;
-                hv.x = __fadd_rn(hv.x, __fmul_rn(__fmul_rn(acc.x, 2.0f), f));
-                hv.y = __fadd_rn(hv.y, __fmul_rn(__fmul_rn(acc.y, 2.0f), f));
-                hv.z = __fadd_rn(hv.z, __fmul_rn(__fmul_rn(acc.z, 2.0f), f));
-                hv.w = __fadd_rn(hv.w, __fmul_rn(__fmul_rn(acc.w, 2.0f), f));
-                *hp = hv;
+            // residual + RMSNorm with unit weight (shader/qwen_norm.comp:55-61,79 op 0)
+#pragma unroll
+            for (uint32_t o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if ((threadIdx.x & 31u) == 0) s_red[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (uint32_t w = 0; w < CB_THREADS / 32; w += 1) tot += s_red[w];
+            float inv = 1.0f / sqrtf(tot / (float)a.d + a.eps);
+            it = 0;
+            for (uint32_t c = threadIdx.x * 4u; c < a.d; c += CB_THREADS * 4u, it += 1) {
+                float4 v = keep[it];
+                __half2 lo = __floats2half2_rn(v.x * inv, v.y * inv);
+                __half2 hi = __floats2half2_rn(v.z * inv, v.w * inv);
+                uint2 out;
+                out.x = *reinterpret_cast<uint32_t *>(&lo);
+                out.y = *reinterpret_cast<uint32_t *>(&hi);
+                *reinterpret_cast<uint2 *>(a.y16 + (size_t)r * a.d + c) = out;
             }
         }
-    }
-    if (NORM) {
-        // residual + RMSNorm with unit weight (shader/qwen_norm.comp:55-61,79 op 0)
-#pragma unroll
-        for (uint32_t o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if ((threadIdx.x & 31u) == 0) s_red[threadIdx.x >> 5] = ss;
-        __syncthreads();
-        float tot = 0.0f;
-#pragma unroll
-        for (uint32_t w = 0; w < CB_THREADS / 32; w += 1) tot += s_red[w];
-        float inv = 1.0f / sqrtf(tot / (float)a.d + a.eps);
-        it = 0;
-        for (uint32_t c = threadIdx.x * 4u; c < a.d; c += CB_THREADS * 4u, it += 1) {
-            float4 v = keep[it];
-            __half2 lo = __floats2half2_rn(v.x * inv, v.y * inv);
-            __half2 hi = __floats2half2_rn(v.z * inv, v.w * inv);
-            uint2 out;
-            out.x = *reinterpret_cast<uint32_t *>(&lo);
-            out.y = *reinterpret_cast<uint32_t *>(&hi);
-            *reinterpret_cast<uint2 *>(a.y16 + (size_t)r * a.d + c) = out;
-        }
+        __syncthreads();  // the row's tables are rewritten by the next pass
     }
 }
 
@@ -171,14 +175,18 @@ void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a) {
     if (a.rows == 0) return;
     const bool peer = a.y_peers != NULL;
     MOE_REQUIRE(c, !peer || a.y_is_f16, "combine: peer rows are fp16");
+    // peer loads beside another token slice's products: at most two blocks (512 threads) per SM, which leaves
+    // room for a grouped-product CTA.  Alone on the GPU the kernel wants every row in flight (a bounded grid
+    // measured 115 us against 47 us for the return of one slice over 2 GPUs).
+    const uint32_t grid = a.bounded_grid && a.rows > (uint32_t)c->sm_count * 2u ? (uint32_t)c->sm_count * 2u : a.rows;
     if (a.y16 != NULL) {
-        if (peer) moe_combine_kernel<__half, true, true><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
-        else if (a.y_is_f16) moe_combine_kernel<__half, true, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
-        else moe_combine_kernel<float, true, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
+        if (peer) moe_combine_kernel<__half, true, true><<<grid, CB_THREADS, 0, c->stream>>>(a);
+        else if (a.y_is_f16) moe_combine_kernel<__half, true, false><<<grid, CB_THREADS, 0, c->stream>>>(a);
+        else moe_combine_kernel<float, true, false><<<grid, CB_THREADS, 0, c->stream>>>(a);
     } else {
-        if (peer) moe_combine_kernel<__half, false, true><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
-        else if (a.y_is_f16) moe_combine_kernel<__half, false, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
-        else moe_combine_kernel<float, false, false><<<a.rows, CB_THREADS, 0, c->stream>>>(a);
+        if (peer) moe_combine_kernel<__half, false, true><<<grid, CB_THREADS, 0, c->stream>>>(a);
+        else if (a.y_is_f16) moe_combine_kernel<__half, false, false><<<grid, CB_THREADS, 0, c->stream>>>(a);
+        else moe_combine_kernel<float, false, false><<<grid, CB_THREADS, 0, c->stream>>>(a);
     }
     MOE_LAUNCHED(c);
 }

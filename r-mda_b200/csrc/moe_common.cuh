@@ -47,6 +47,8 @@ struct moe_cuda_ctx {
     bool prof;
     cudaEvent_t ev[MOE_PROF_STAGES + 1];
     bool ev_made, ev_valid;
+    cudaEvent_t ev_mb[3][MOE_PROF_STAGES + 1];  // expert parallel: the same marks of token slices 1..3, on their streams
+    int ev_mb_made, ev_slices;
     uint64_t launches;
     int fail_alloc_countdown;
     bool mm_attr_set[4];
@@ -114,7 +116,7 @@ void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
                       void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row = NULL,
                       uint32_t *const *src_row_peers = NULL, uint32_t src_base = 0, uint2 *const *ret_peers = NULL,
-                      const float *wt = NULL);
+                      const float *wt = NULL, bool bounded_grid = false);
 
 enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // Grouped product.  mode F32: C fp32 [m x n] = A*B^T * s;  SWIGLU_F16: B holds
@@ -156,6 +158,7 @@ struct moe_combine_args {
     uint32_t world;      // number of GPUs behind y_peers
     uint32_t src_base;
     bool per_gpu;
+    bool bounded_grid;   // launch at most two blocks per SM (the kernel shares the GPU with another slice's products)
 };
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a);
 void moe_overlap_prepare_combine(moe_cuda_ctx *c);

@@ -96,6 +96,9 @@ extern "C" void moe_cuda_destroy(moe_cuda_ctx_t *c) {
     if (c->ev_made) {
         for (int i = 0; i <= MOE_PROF_STAGES; i += 1) cudaEventDestroy(c->ev[i]);
     }
+    for (int m = 0; m < c->ev_mb_made; m += 1) {
+        for (int i = 0; i <= MOE_PROF_STAGES; i += 1) cudaEventDestroy(c->ev_mb[m][i]);
+    }
     if (c->ticket != NULL) cudaFree(c->ticket);
     if (c->dev_status_host != NULL) cudaFreeHost(c->dev_status_host);
     if (c->own_stream) cudaStreamDestroy(c->stream);
@@ -273,9 +276,14 @@ extern "C" void moe_cuda_prof(moe_cuda_ctx_t *c, int on) {
 extern "C" void moe_cuda_prof_read(moe_cuda_ctx_t *c, float ms[MOE_PROF_STAGES]) {
     for (int i = 0; i < MOE_PROF_STAGES; i += 1) ms[i] = 0.0f;
     if (!MOE_LIVE(c) || !c->ev_valid) return;
-    MOE_CUDA_TRY(c, cudaEventSynchronize(c->ev[MOE_PROF_STAGES]));
-    for (int i = 0; i < MOE_PROF_STAGES; i += 1) {
-        MOE_CUDA_TRY(c, cudaEventElapsedTime(&ms[i], c->ev[i], c->ev[i + 1]));
+    MOE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));  // the slices' streams have joined the context's stream
+    for (int m = 0; m < (c->ev_slices > 1 ? c->ev_slices : 1); m += 1) {
+        cudaEvent_t *ev = m == 0 ? c->ev : c->ev_mb[m - 1];
+        for (int i = 0; i < MOE_PROF_STAGES; i += 1) {
+            float t = 0.0f;
+            MOE_CUDA_TRY(c, cudaEventElapsedTime(&t, ev[i], ev[i + 1]));
+            ms[i] += t;
+        }
     }
 }
 

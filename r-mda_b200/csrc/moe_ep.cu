@@ -83,9 +83,9 @@ static bool moe_nccl_load(char *why, size_t n) {
 }
 
 #define MOE_EP_MAX_WORLD 16
-#define EP_FLAG_WORDS 128u  // 6 barrier sites (3 per micro-batch) x 16 ranks of epoch flags, padded
+#define EP_FLAG_WORDS 256u  // 16 barrier sites x 16 ranks of epoch flags: 3 per micro-batch, the last one for teardown
 
-#define EP_MAX_MB 2  // micro-batches per layer call
+#define EP_MAX_MB 4  // micro-batches per layer call
 
 struct moe_ep_state {
     ncclComm_t comm;
@@ -117,8 +117,9 @@ struct moe_ep_state {
     uint32_t *count[EP_MAX_MB];
     uint32_t *idx, *slot, *bar;
     float *wt;
-    cudaStream_t side;                   // second stream: micro-batch 1
-    cudaEvent_t ev_fork, ev_disp, ev_join;
+    cudaStream_t side[EP_MAX_MB];        // streams of micro-batches 1.. (micro-batch 0 runs on the context's stream)
+    cudaEvent_t ev_fork, ev_disp[EP_MAX_MB], ev_join[EP_MAX_MB];
+    bool streams_made;
 };
 
 #define MOE_NCCL_TRY(c, expr)                                                                   \
@@ -157,7 +158,7 @@ __global__ void moe_ep_barrier_kernel(uint32_t *const *sync_peers, uint32_t worl
 // bounded flag barrier (its own site) first.  A failed context cannot know what
 // its peers still have in flight: it closes its mappings of their memory but
 // leaves its own exported buffers allocated until the process exits.
-#define EP_SITE_TEARDOWN 6u
+#define EP_SITE_TEARDOWN 15u
 void moe_ep_teardown(moe_cuda_ctx *c) {
     if (c == NULL || c->ep == NULL) return;
     moe_ep_state *ep = c->ep;
@@ -179,17 +180,26 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
         if (ep->yout_peer[r] != NULL) cudaIpcCloseMemHandle(ep->yout_peer[r]);
         if (ep->sync_peer[r] != NULL) cudaIpcCloseMemHandle(ep->sync_peer[r]);
     }
-    void *mine[] = {ep->xin, ep->yout, ep->ye, ep->hp16, ep->xin_peer_dev[0], ep->yout_peer_dev[0], ep->xin_peer_dev[1], ep->yout_peer_dev[1],
-                    ep->srow_peer_dev[0], ep->srow_peer_dev[1], ep->ret_peer_dev[0], ep->ret_peer_dev[1], ep->sync_peer_dev, ep->sync, ep->dst_off[0], ep->dst_off[1], ep->tiles[0], ep->tiles[1], ep->count[0],
-                    ep->count[1], ep->idx, ep->slot, ep->bar, ep->wt};
-    if (ep->side != NULL) {
-        cudaStreamSynchronize(ep->side);
-        cudaStreamDestroy(ep->side);
-        cudaEventDestroy(ep->ev_fork);
-        cudaEventDestroy(ep->ev_disp);
-        cudaEventDestroy(ep->ev_join);
+    void *mine[10 + 7 * EP_MAX_MB] = {ep->xin, ep->yout, ep->ye, ep->hp16, ep->sync_peer_dev, ep->sync, ep->idx, ep->slot};
+    size_t n_mine = 8;
+    mine[n_mine++] = ep->bar;
+    mine[n_mine++] = ep->wt;
+    for (uint32_t m = 0; m < EP_MAX_MB; m += 1) {
+        void *per[] = {ep->xin_peer_dev[m], ep->yout_peer_dev[m], ep->srow_peer_dev[m], ep->ret_peer_dev[m], ep->dst_off[m], ep->tiles[m], ep->count[m]};
+        for (size_t i = 0; i < sizeof(per) / sizeof(per[0]) && n_mine < sizeof(mine) / sizeof(mine[0]); i += 1) mine[n_mine++] = per[i];
     }
-    for (size_t i = 0; i < sizeof(mine) / sizeof(mine[0]); i += 1) {
+    if (ep->streams_made) {
+        cudaEventDestroy(ep->ev_fork);
+        for (uint32_t m = 0; m < ep->nmb; m += 1) {
+            if (m != 0 && ep->side[m] != NULL) {
+                cudaStreamSynchronize(ep->side[m]);
+                cudaStreamDestroy(ep->side[m]);
+            }
+            if (ep->ev_disp[m] != NULL) cudaEventDestroy(ep->ev_disp[m]);
+            if (ep->ev_join[m] != NULL) cudaEventDestroy(ep->ev_join[m]);
+        }
+    }
+    for (size_t i = 0; i < n_mine; i += 1) {
         const bool exported = mine[i] == (void *)ep->xin || mine[i] == (void *)ep->yout || mine[i] == (void *)ep->sync;
         if (mine[i] != NULL && (rendezvous || !exported)) cudaFree(mine[i]);
     }
@@ -241,7 +251,7 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
     // (0.672 against 0.712 at 8 GPUs); with per-GPU transfers one slice measured faster (0.610
     // against 0.617 at 4 GPUs, 0.512 against 0.572 at 2)
     uint32_t nmb = cfg->micro_batches != 0 ? cfg->micro_batches : ((world >= 4 && !per_gpu) ? 2u : 1u);
-    uint32_t rows_mb = nmb == 1 ? cfg->max_rows : (((cfg->max_rows + 1u) / 2u + 7u) & ~7u);
+    uint32_t rows_mb = nmb == 1 ? cfg->max_rows : (((cfg->max_rows + nmb - 1u) / nmb + 7u) & ~7u);
     uint32_t mcap = moe_cuda_ep_rows((uint32_t)world, rows_mb, cfg->experts, cfg->topk);
     MOE_REQUIRE(c, mcap != 0, "ep_init: buffer rows overflow");
     moe_ep_state *ep = (moe_ep_state *)calloc(1, sizeof(moe_ep_state));
@@ -312,10 +322,13 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
         MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_barrier_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_ep_plan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         if (c->status != MOE_OK) return;
-        MOE_CUDA_TRY(c, cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking));
+        ep->streams_made = true;
         MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_fork, cudaEventDisableTiming));
-        MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_disp, cudaEventDisableTiming));
-        MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_join, cudaEventDisableTiming));
+        for (uint32_t m = 0; m < nmb; m += 1) {
+            if (m != 0) MOE_CUDA_TRY(c, cudaStreamCreateWithFlags(&ep->side[m], cudaStreamNonBlocking));
+            MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_disp[m], cudaEventDisableTiming));
+            MOE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep->ev_join[m], cudaEventDisableTiming));
+        }
     }
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->bar, 0, 256, c->stream));
     MOE_CUDA_TRY(c, cudaMemsetAsync(ep->sync, 0, sync_words * 4, c->stream));
@@ -583,6 +596,16 @@ moe_ep_partial_kernel(const uint2 *__restrict__ ret_tab, const uint4 *__restrict
     }
 }
 
+// Rows of micro-batch m when `rows` tokens are cut into nmb slices: equal parts rounded up to the router's
+// 8-row blocks, the last slice takes what is left (possibly nothing).
+static void ep_slice(uint32_t rows, uint32_t nmb, uint32_t m, uint32_t *row0, uint32_t *n) {
+    const uint32_t part = nmb == 1 ? rows : (((rows + nmb - 1u) / nmb + 7u) & ~7u);
+    const uint32_t lo = (uint64_t)m * part < rows ? m * part : rows;
+    const uint32_t hi = m + 1u == nmb ? rows : ((uint64_t)(m + 1u) * part < rows ? (m + 1u) * part : rows);
+    *row0 = lo;
+    *n = hi - lo;
+}
+
 extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
     if (!MOE_LIVE(c)) return;
     moe_ep_state *ep = c->ep;
@@ -592,19 +615,31 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
     MOE_REQUIRE(c, L->experts == ep->cfg.experts && L->topk == ep->cfg.topk && L->d == ep->cfg.d && L->inter == ep->cfg.inter,
                 "ep_layer: shape differs from moe_cuda_ep_init");
     MOE_REQUIRE(c, L->rows <= ep->cfg.max_rows, "ep_layer: rows %u > max_rows %u", L->rows, ep->cfg.max_rows);
-    MOE_REQUIRE(c, L->shared == 0, "ep_layer: the shared expert is not part of the expert-parallel path");
+    MOE_REQUIRE(c, L->shared % 128u == 0, "ep_layer: shared %u not a multiple of 128", L->shared);
+    MOE_REQUIRE(c, L->shared == 0 || (L->wsgu != NULL && L->wsdown != NULL), "ep_layer: shared expert without weights");
     MOE_REQUIRE(c, L->hc >= 1, "ep_layer: hc 0");
-    const uint32_t R = L->rows, K = L->topk, E = L->experts, d = L->d, I = L->inter;
+    const uint32_t R = L->rows, K = L->topk, E = L->experts, d = L->d, I = L->inter, S = L->shared;
     const uint32_t mcap = ep->mcap, nmb = ep->nmb;
     uint32_t *idx = L->idx != NULL ? L->idx : ep->idx;
     uint32_t *slot = L->slot != NULL ? L->slot : ep->slot;
     float *wt = L->wt != NULL ? L->wt : ep->wt;
     cudaStream_t main_stream = c->stream;
+    const bool prof = c->prof && c->ev_made;
+    // with several token slices in flight the transfer kernels leave room for the other slices' products
+    bool bound = nmb > 1;
+    if (getenv("MOE_EP_BOUND_GRID") != NULL) bound = atoi(getenv("MOE_EP_BOUND_GRID")) != 0;
 
-    auto mark = [&](int i) {
-        if (c->prof && c->ev_made && c->status == MOE_OK) cudaEventRecord(c->ev[i], main_stream);
+    // stage marks of micro-batch m go on its own stream; moe_cuda_prof_read adds the slices up
+    auto mark = [&](uint32_t m, int i) {
+        if (prof && c->status == MOE_OK) cudaEventRecord(m == 0 ? c->ev[i] : c->ev_mb[m - 1][i], c->stream);
     };
-    mark(0);
+    if (prof && nmb > 1 && c->ev_mb_made < (int)nmb - 1) {
+        for (int m = c->ev_mb_made; m < (int)nmb - 1; m += 1) {
+            for (int i = 0; i <= MOE_PROF_STAGES; i += 1) MOE_CUDA_TRY(c, cudaEventCreate(&c->ev_mb[m][i]));
+            c->ev_mb_made = m + 1;
+        }
+    }
+    mark(0, 0);
     for (uint32_t m = 0; m < nmb; m += 1) {
         moe_cuda_fill(c, ep->tiles[m], (size_t)(mcap / MOE_TILE) * 4, 0xffffffffu);
         if (ep->per_gpu) {
@@ -616,21 +651,37 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
     }
     uint32_t *hist = (uint32_t *)moe_scratch(c, MOE_SCR_SCATTER, (size_t)((R + 7u) / 8u + 1u) * E * 4);
     if (hist == NULL) return;
+    // The shared expert (src/qwen.c:879-886) is replicated: every rank runs it on its own tokens.
+    const uint32_t Rp = (R + MOE_TILE - 1u) / MOE_TILE * MOE_TILE;
+    __half *hs16 = NULL;
+    float *sh = NULL;
+    uint32_t *tiles0 = NULL;
+    if (S != 0 && R != 0) {
+        const size_t b_hs = ((size_t)Rp * S * 2 + 1023) & ~(size_t)1023, b_sh = ((size_t)Rp * d * 4 + 1023) & ~(size_t)1023;
+        uint8_t *scr = (uint8_t *)moe_scratch(c, MOE_SCR_LAYER, b_hs + b_sh + (size_t)(Rp / MOE_TILE) * 4 + 1024);
+        if (scr == NULL) return;
+        hs16 = (__half *)scr;
+        sh = (float *)(scr + b_hs);
+        tiles0 = (uint32_t *)(scr + b_hs + b_sh);
+    }
     if (R != 0) moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride);
-    mark(1);
+    mark(0, 1);
     if (!MOE_LIVE(c)) return;
     ep->epoch += 1;
-    // rows of micro-batch 0: the first half, rounded to the router's 8-row blocks
-    const uint32_t r0 = nmb == 1 ? R : (R < (((R + 1u) / 2u + 7u) & ~7u) ? R : (((R + 1u) / 2u + 7u) & ~7u));
     if (nmb > 1) {
         MOE_CUDA_TRY(c, cudaEventRecord(ep->ev_fork, main_stream));
-        MOE_CUDA_TRY(c, cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
+        for (uint32_t m = 1; m < nmb; m += 1) MOE_CUDA_TRY(c, cudaStreamWaitEvent(ep->side[m], ep->ev_fork, 0));
     }
     for (uint32_t m = 0; m < nmb; m += 1) {
         // Micro-batch m runs on its own stream; every rank issues the same sequence, also for an empty slice.
-        const uint32_t row0 = m == 0 ? 0u : r0, rows = m == 0 ? r0 : R - r0;
+        uint32_t row0, rows;
+        ep_slice(R, nmb, m, &row0, &rows);
         const uint32_t site = 3u * m;
-        c->stream = m == 0 ? main_stream : ep->side;
+        c->stream = m == 0 ? main_stream : ep->side[m];
+        if (m != 0) {
+            mark(m, 0);
+            mark(m, 1);
+        }
         uint32_t *count = (m == 0 && nmb == 1 && L->count != NULL) ? L->count : ep->count[m];
         if (rows != 0) moe_launch_colscan_counts(c, hist + (size_t)(row0 / 8u) * E, count, rows, E);
         else moe_cuda_fill(c, count, (size_t)E * 4, 0);
@@ -639,20 +690,17 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
                                                      EP_FLAG_WORDS + m * (uint32_t)ep->world * E, ep->dst_off[m], ep->tiles[m], E,
                                                      (uint32_t)ep->world, (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev, c->wait_ns);
         c->launches += 1;
-        if (m == 0) {
-            if (L->off != NULL && nmb == 1) moe_cuda_copy(c, L->off, ep->dst_off[0], (size_t)E * 4);
-            mark(2);
-        } else {
-            // stagger: this slice's rows go out once the first slice's are on their way, under its products
-            cudaStreamWaitEvent(c->stream, ep->ev_disp, 0);
-        }
+        if (m == 0 && L->off != NULL && nmb == 1) moe_cuda_copy(c, L->off, ep->dst_off[0], (size_t)E * 4);
+        mark(m, 2);
+        // stagger: this slice's rows go out once the previous slice's are on their way, under its products
+        if (m != 0) cudaStreamWaitEvent(c->stream, ep->ev_disp[m - 1], 0);
         __half *xin_m = ep->xin + (size_t)m * ep->in_rows * d, *yout_m = ep->yout + (size_t)m * ep->in_rows * d;
         __half *ye_m = ep->per_gpu ? ep->ye + (size_t)m * mcap * d : yout_m;
         if (rows != 0 && !ep->per_gpu) {
             // dispatch fused into the scatter: every pair's row goes straight into its owner's expert-contiguous buffer
             moe_launch_place(c, idx + (size_t)row0 * K, ep->dst_off[m], hist + (size_t)(row0 / 8u) * E,
                              (const __half *)L->x16 + (size_t)row0 * d, xin_m, slot + (size_t)row0 * K, rows, K, d / 8u, E,
-                             ep->xin_peer_dev[m], ep->el);
+                             ep->xin_peer_dev[m], ep->el, NULL, NULL, 0, NULL, NULL, bound);
         }
         // dispatch: each row once per destination GPU, then the records of every (token, expert) pair
         if (rows != 0 && ep->per_gpu) {
@@ -666,14 +714,24 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
                              (uint32_t *const *)ep->srow_peer_dev[m], src_base, (uint2 *const *)ep->ret_peer_dev[m],
                              wt + (size_t)row0 * K);
         }
-        if (m == 0 && nmb > 1) cudaEventRecord(ep->ev_disp, c->stream);
+        if (nmb > 1) cudaEventRecord(ep->ev_disp[m], c->stream);
+        if (m == 0 && S != 0 && R != 0) {
+            // the shared expert's two products on all local tokens, while the other ranks' rows are still landing
+            moe_cuda_fill(c, tiles0, (size_t)(Rp / MOE_TILE) * 4, 0);
+            moe_launch_mm(c, MOE_MM_SWIGLU_F16, L->x16, L->wsgu, hs16, NULL, tiles0, Rp, 2u * S, d, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, 1, R);
+            moe_launch_mm(c, MOE_MM_F32, hs16, L->wsdown, sh, NULL, tiles0, Rp, d, S, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, 1, Rp);
+            if (nmb > 1) {  // the other slices' combines read sh too
+                MOE_CUDA_TRY(c, cudaEventRecord(ep->ev_join[0], c->stream));
+                for (uint32_t q = 1; q < nmb; q += 1) MOE_CUDA_TRY(c, cudaStreamWaitEvent(ep->side[q], ep->ev_join[0], 0));
+            }
+        }
         moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
                                                        (uint32_t)ep->rank, site + 1u, ep->epoch, c->dev_status_dev, c->wait_ns);  // all rows landed
         c->launches += 1;
-        if (m == 0) mark(3);
+        mark(m, 3);
         moe_launch_mm(c, MOE_MM_SWIGLU_F16, xin_m, L->wgu, ep->hp16 + (size_t)m * mcap * I, NULL, ep->tiles[m], mcap, 2u * I, d,
                       MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, ep->in_rows, true, ep->per_gpu ? ep->src_row[m] : NULL);
-        if (m == 0) mark(4);
+        mark(m, 4);
         moe_launch_mm(c, MOE_MM_F16, ep->hp16 + (size_t)m * mcap * I, L->wdown, ye_m, NULL,
                       ep->tiles[m], mcap, d, I, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);
         if (ep->per_gpu) {  // return, owner side: one weighted partial row per received token
@@ -683,17 +741,18 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
                 ep->ret_tab[m], (const uint4 *)ye_m, (uint4 *)yout_m, slots, K, d / 8u);
             c->launches += 1;
         }
-        if (m == 0) mark(5);
+        mark(m, 5);
         moe_ep_barrier_kernel<<<1, 32, 0, c->stream>>>((uint32_t *const *)ep->sync_peer_dev, (uint32_t)ep->world,
                                                        (uint32_t)ep->rank, site + 2u, ep->epoch, c->dev_status_dev, c->wait_ns);  // all result rows written
         c->launches += 1;
-        if (m == 0) mark(6);
+        mark(m, 6);
         if (rows != 0) {
             moe_combine_args a = {};
             a.wt = wt + (size_t)row0 * K;
             a.slot = slot + (size_t)row0 * K;
             a.y = ye_m;
             a.proj = L->proj + (size_t)row0 * L->pstride;
+            a.sh = S != 0 ? sh + (size_t)row0 * d : NULL;
             a.inj = L->inj != NULL ? L->inj + (size_t)row0 * L->inj_stride : NULL;
             a.h = L->h != NULL ? L->h + (size_t)row0 * L->hc * d : NULL;
             a.x16 = (const __half *)L->x16 + (size_t)row0 * d;
@@ -714,15 +773,19 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             a.world = (uint32_t)ep->world;
             a.src_base = (uint32_t)ep->rank * ep->cap;
             a.per_gpu = ep->per_gpu;
+            a.bounded_grid = bound;
             moe_launch_combine(c, a);  // return all-to-all fused into the gather: one partial row per owning GPU
         }
-        if (m == 0) mark(7);
+        mark(m, 7);
     }
     c->stream = main_stream;
-    if (nmb > 1) {
-        cudaEventRecord(ep->ev_join, ep->side);
-        cudaStreamWaitEvent(main_stream, ep->ev_join, 0);
+    for (uint32_t m = 1; m < nmb; m += 1) {
+        cudaEventRecord(ep->ev_join[m], ep->side[m]);
+        cudaStreamWaitEvent(main_stream, ep->ev_join[m], 0);
     }
     if (cudaGetLastError() != cudaSuccess) moe_fail(c, MOE_ERR_CUDA, "ep_layer: launch failed");
-    if (c->prof && c->ev_made && c->status == MOE_OK) c->ev_valid = true;
+    if (prof && c->status == MOE_OK) {
+        c->ev_valid = true;
+        c->ev_slices = (int)nmb;
+    }
 }

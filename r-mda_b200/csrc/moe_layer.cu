@@ -227,5 +227,8 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
     a.y_is_f16 = !ye32;
     moe_launch_combine(c, a);  // :887-906
     mark(c, 7);
-    if (c->prof && c->ev_made && c->status == MOE_OK) c->ev_valid = true;
+    if (c->prof && c->ev_made && c->status == MOE_OK) {
+        c->ev_valid = true;
+        c->ev_slices = 1;
+    }
 }

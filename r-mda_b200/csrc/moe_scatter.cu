@@ -115,63 +115,70 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
                          uint32_t d8, uint32_t ebound, uint4 *const *__restrict__ xp_peers, uint32_t experts_per_rank,
                          uint32_t ppb, uint32_t *__restrict__ src_row, uint32_t *const *__restrict__ src_row_peers,
                          uint32_t src_base, uint2 *const *__restrict__ ret_peers, const float *__restrict__ wt) {
-    // ppb = pairs per block (<= SC_MAX_PAIRS): 64 in the stand-alone scatter, 8*topk behind the fused router
+    // ppb = pairs per block (<= SC_MAX_PAIRS): 64 in the stand-alone scatter, 8*topk behind the fused router.
+    // A block takes pair groups blockIdx.x, blockIdx.x + gridDim.x, ...: the expert-parallel layer launches a
+    // bounded grid so that this kernel's peer stores can share the SMs with a resident grouped-product CTA.
     __shared__ uint32_t s_e[SC_MAX_PAIRS];
     __shared__ uint32_t s_slot[SC_MAX_PAIRS];
     __shared__ uint4 *s_dst[SC_MAX_PAIRS];
-    uint32_t p0 = blockIdx.x * ppb;
-    uint32_t np = min(ppb, pairs - p0);
-    if (threadIdx.x < SC_MAX_PAIRS) s_e[threadIdx.x] = threadIdx.x < np ? idx[p0 + threadIdx.x] : ~0u;
-    __syncthreads();
-    if (threadIdx.x < np) {
-        uint32_t e = s_e[threadIdx.x];
-        if (e < ebound) {
-            uint32_t rank = 0;
-            for (uint32_t q = 0; q < threadIdx.x; q += 1) rank += s_e[q] == e;
-            uint32_t p = off[e] + base[(size_t)blockIdx.x * ebound + e] + rank;
-            s_slot[threadIdx.x] = p;
-            // expert-parallel: the row goes straight into the owning GPU's buffer over NVLink
-            s_dst[threadIdx.x] = xp_peers != NULL ? xp_peers[e / experts_per_rank] : xp;
-            slot[p0 + threadIdx.x] = p;  // :27
-            // gather mode: record where the row comes from instead of copying it; the product fetches it
-            if (src_row != NULL) src_row[p] = (p0 + threadIdx.x) / topk;
-            // expert-parallel gather mode: the record goes into the owning GPU's table; the row itself
-            // travels once per destination GPU (moe_ep_send_kernel) and sits at src_base + its local index
-            else if (src_row_peers != NULL) {
-                const uint32_t g = e / experts_per_rank, row = src_base + (p0 + threadIdx.x) / topk;
-                src_row_peers[g][p] = row;
-                if (ret_peers != NULL) {
-                    // return record: (row of the expert's output, router weight), the token's records on one
-                    // GPU packed in j order (ppb is a multiple of topk, so a token's pairs share the block)
-                    const uint32_t t0 = threadIdx.x - threadIdx.x % topk;
-                    uint32_t jj = 0;
-                    for (uint32_t q = t0; q < threadIdx.x; q += 1) jj += (s_e[q] < ebound && s_e[q] / experts_per_rank == g) ? 1u : 0u;
-                    ret_peers[g][(size_t)row * topk + jj] = make_uint2(p, __float_as_uint(wt[p0 + threadIdx.x]));
+    const uint32_t ngroups = (pairs + ppb - 1u) / ppb;
+    for (uint32_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
+        uint32_t p0 = grp * ppb;
+        uint32_t np = min(ppb, pairs - p0);
+        if (threadIdx.x < SC_MAX_PAIRS) s_e[threadIdx.x] = threadIdx.x < np ? idx[p0 + threadIdx.x] : ~0u;
+        __syncthreads();
+        if (threadIdx.x < np) {
+            uint32_t e = s_e[threadIdx.x];
+            if (e < ebound) {
+                uint32_t rank = 0;
+                for (uint32_t q = 0; q < threadIdx.x; q += 1) rank += s_e[q] == e;
+                uint32_t p = off[e] + base[(size_t)grp * ebound + e] + rank;
+                s_slot[threadIdx.x] = p;
+                // expert-parallel: the row goes straight into the owning GPU's buffer over NVLink
+                s_dst[threadIdx.x] = xp_peers != NULL ? xp_peers[e / experts_per_rank] : xp;
+                slot[p0 + threadIdx.x] = p;  // :27
+                // gather mode: record where the row comes from instead of copying it; the product fetches it
+                if (src_row != NULL) src_row[p] = (p0 + threadIdx.x) / topk;
+                // expert-parallel gather mode: the record goes into the owning GPU's table; the row itself
+                // travels once per destination GPU (moe_ep_send_kernel) and sits at src_base + its local index
+                else if (src_row_peers != NULL) {
+                    const uint32_t g = e / experts_per_rank, row = src_base + (p0 + threadIdx.x) / topk;
+                    src_row_peers[g][p] = row;
+                    if (ret_peers != NULL) {
+                        // return record: (row of the expert's output, router weight), the token's records on one
+                        // GPU packed in j order (ppb is a multiple of topk, so a token's pairs share the block)
+                        const uint32_t t0 = threadIdx.x - threadIdx.x % topk;
+                        uint32_t jj = 0;
+                        for (uint32_t q = t0; q < threadIdx.x; q += 1) jj += (s_e[q] < ebound && s_e[q] / experts_per_rank == g) ? 1u : 0u;
+                        ret_peers[g][(size_t)row * topk + jj] = make_uint2(p, __float_as_uint(wt[p0 + threadIdx.x]));
+                    }
                 }
+            } else {
+                s_slot[threadIdx.x] = ~0u;
+                slot[p0 + threadIdx.x] = ~0u;  // a pair the router refused: the combine skips it
             }
-        } else {
-            s_slot[threadIdx.x] = ~0u;
-            slot[p0 + threadIdx.x] = ~0u;  // a pair the router refused: the combine skips it
         }
-    }
-    if (src_row != NULL || src_row_peers != NULL) return;
-    __syncthreads();
-    uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    for (uint32_t q = warp; q < np; q += SC_THREADS / 32u) {
-        uint32_t p = s_slot[q];
-        if (p == ~0u) continue;
-        uint32_t r = (p0 + q) / topk;  // :20
-        const uint4 *src = x16 + (size_t)r * d8;
-        uint4 *dst = s_dst[q] + (size_t)p * d8;
-        uint32_t i = lane;
-        for (; i + 96u < d8; i += 128u) {  // four 16-byte loads in flight per lane
-            uint4 a = __ldg(src + i), b = __ldg(src + i + 32u), c2 = __ldg(src + i + 64u), d2 = __ldg(src + i + 96u);
-            dst[i] = a;
-            dst[i + 32u] = b;
-            dst[i + 64u] = c2;
-            dst[i + 96u] = d2;
+        __syncthreads();
+        if (src_row == NULL && src_row_peers == NULL) {
+            uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+            for (uint32_t q = warp; q < np; q += SC_THREADS / 32u) {
+                uint32_t p = s_slot[q];
+                if (p == ~0u) continue;
+                uint32_t r = (p0 + q) / topk;  // :20
+                const uint4 *src = x16 + (size_t)r * d8;
+                uint4 *dst = s_dst[q] + (size_t)p * d8;
+                uint32_t i = lane;
+                for (; i + 96u < d8; i += 128u) {  // four 16-byte loads in flight per lane
+                    uint4 a = __ldg(src + i), b = __ldg(src + i + 32u), c2 = __ldg(src + i + 64u), d2 = __ldg(src + i + 96u);
+                    dst[i] = a;
+                    dst[i + 32u] = b;
+                    dst[i + 64u] = c2;
+                    dst[i + 96u] = d2;
+                }
+                for (; i < d8; i += 32u) dst[i] = __ldg(src + i);  // :30-32
+            }
+            __syncthreads();  // the tables are rewritten by the next group
         }
-        for (; i < d8; i += 32u) dst[i] = __ldg(src + i);  // :30-32
     }
 }
 
@@ -232,11 +239,14 @@ void moe_overlap_prepare_scatter(moe_cuda_ctx *c) {
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
                       void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row, uint32_t *const *src_row_peers,
-                      uint32_t src_base, uint2 *const *ret_peers, const float *wt) {
+                      uint32_t src_base, uint2 *const *ret_peers, const float *wt, bool bounded_grid) {
     if (!MOE_LIVE(c)) return;
     if (rows == 0) return;
     MOE_REQUIRE(c, ((uintptr_t)x16 & 15) == 0 && ((uintptr_t)xp & 15) == 0, "scatter: rows not 16-byte aligned");
     uint32_t nblocks = (rows + 7u) / 8u;
+    // Beside another token slice's products: two blocks (512 threads) per SM at most, so that a grouped-product
+    // CTA still fits beside them; an SM full of these blocks would keep the product waiting.
+    if (bounded_grid && nblocks > (uint32_t)c->sm_count * 2u) nblocks = (uint32_t)c->sm_count * 2u;
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp, slot,
                                                                     rows * topk, topk, d8, experts,
                                                                     (uint4 *const *)xp_peers, experts_per_rank, 8u * topk, src_row,

@@ -15,6 +15,18 @@ def ep_rows(world: int, max_rows: int, experts: int, topk: int) -> int:
     return (n + TILE - 1) // TILE * TILE
 
 
+def slices(rows: int, nmb: int):
+    """Row ranges of the token slices `moe_cuda_ep_layer` cuts `rows` tokens into: equal parts rounded
+    up to the router's 8-row blocks, the last slice takes the rest (possibly nothing)."""
+    part = rows if nmb == 1 else ((rows + nmb - 1) // nmb + 7) // 8 * 8
+    out = []
+    for m in range(nmb):
+        lo = min(m * part, rows)
+        hi = rows if m == nmb - 1 else min((m + 1) * part, rows)
+        out.append((lo, hi))
+    return out
+
+
 def plan(cnt_all: np.ndarray, rank: int):
     """cnt_all [G, E]: pairs of each source rank per global expert.  Returns
     dst_off [E] (first row of `rank`'s rows of expert e inside the owner's buffer),

@@ -24,15 +24,18 @@ def main():
     ok = True
     cache = {}
     # transfer 1: one row per (token, expert) pair each way; 2: one row per (token, owning GPU)
-    for T_local, E, K, d, I, beta, nmb, transfer in [
-            (300, 32, 4, 512, 256, 0.0, 1, 1), (300, 32, 4, 512, 256, 0.0, 2, 1),
-            (300, 32, 4, 512, 256, 0.0, 1, 2), (300, 32, 4, 512, 256, 0.0, 2, 2),
-            (1024, 128, 8, 2048, 768, 1.0, 0, 1), (1024, 128, 8, 2048, 768, 1.0, 2, 2), (1024, 128, 8, 2048, 768, 1.0, 0, 0)]:
-        key = (T_local, E, K, d, I, beta)
+    # (tokens per rank, E, K, d, I, shared S, Zipf beta, token slices, transfer)
+    for T_local, E, K, d, I, S, beta, nmb, transfer in [
+            (300, 32, 4, 512, 256, 0, 0.0, 1, 1), (300, 32, 4, 512, 256, 0, 0.0, 2, 1),
+            (300, 32, 4, 512, 256, 0, 0.0, 1, 2), (300, 32, 4, 512, 256, 0, 0.0, 2, 2),
+            (300, 32, 4, 512, 256, 0, 0.0, 4, 1), (300, 32, 4, 512, 256, 128, 0.0, 3, 1), (300, 32, 4, 512, 256, 128, 0.0, 1, 2),
+            (1024, 128, 8, 2048, 768, 0, 1.0, 0, 1), (1024, 128, 8, 2048, 768, 0, 1.0, 2, 2), (1024, 128, 8, 2048, 768, 0, 1.0, 0, 0),
+            (1024, 128, 8, 2048, 768, 256, 0.0, 4, 1)]:
+        key = (T_local, E, K, d, I, S, beta)
         if key not in cache:
-            cfg = dataclasses.replace(synth.CONFIGS["c1"], T=T_local * world, E=E, K=K, d=d, I=I, zipf_beta=beta)
+            cfg = dataclasses.replace(synth.CONFIGS["c1"], T=T_local * world, E=E, K=K, d=d, I=I, S=S, zipf_beta=beta)
             inp = synth.layer_inputs(cfg, 7)
-            cache = {key: (cfg, inp, O.layer(inp.proj, inp.x16, inp.wgu, inp.wdown, K))}
+            cache = {key: (cfg, inp, O.layer(inp.proj, inp.x16, inp.wgu, inp.wdown, K, inp.wsgu, inp.wsdown))}
         cfg, inp, full = cache[key]
         el = E // world
         lo, hi = rank * T_local, (rank + 1) * T_local
@@ -40,11 +43,10 @@ def main():
         dist.broadcast_object_list(uid, src=0)
         per_gpu = transfer == 2 or (transfer == 0 and world <= 4)
         eff_mb = nmb if nmb else (2 if (world >= 4 and not per_gpu) else 1)   # the library's automatic choice
-        r0 = T_local if eff_mb == 1 else min(T_local, ((T_local + 1) // 2 + 7) // 8 * 8)
         # expected rows: inside the owner's buffer of the token's micro-batch, rows of an expert are ordered
         # (source rank, token) -- the single-device order restricted to that micro-batch
         want = np.empty((T_local, K), np.int64)
-        for m, (a, b) in enumerate([(0, r0), (r0, T_local)][:eff_mb]):
+        for m, (a, b) in enumerate(epp.slices(T_local, eff_mb)):
             cnt_m = np.stack([np.bincount(full.idx[r * T_local + a:r * T_local + b].ravel(), minlength=E)
                               for r in range(world)]).astype(np.uint32)
             dst_off = epp.plan(cnt_m, rank)[0]
@@ -55,11 +57,14 @@ def main():
             d_proj, d_x = ctx.upload(np.ascontiguousarray(inp.proj[lo:hi])), ctx.upload(np.ascontiguousarray(inp.x16[lo:hi]))
             d_wgu = ctx.upload(np.ascontiguousarray(inp.wgu[rank * el:(rank + 1) * el]))
             d_wdown = ctx.upload(np.ascontiguousarray(inp.wdown[rank * el:(rank + 1) * el]))
+            d_wsgu = ctx.upload(inp.wsgu) if S else None
+            d_wsdown = ctx.upload(inp.wsdown) if S else None
             d_idx, d_slot, d_wt = ctx.alloc(T_local * K * 4), ctx.alloc(T_local * K * 4), ctx.alloc(T_local * K * 4)
             for rep in range(2):    # the second pass reuses the peer buffers
                 d_h = ctx.zeros(T_local * d * 4)
-                ctx.ep_layer(rows=T_local, d=d, experts=E, topk=K, inter=I, shared=0, pstride=cfg.pstride, hc=1,
-                             proj=d_proj, x16=d_x, wgu=d_wgu, wdown=d_wdown, h=d_h, idx=d_idx, slot=d_slot, wt=d_wt)
+                ctx.ep_layer(rows=T_local, d=d, experts=E, topk=K, inter=I, shared=S, pstride=cfg.pstride, hc=1,
+                             proj=d_proj, x16=d_x, wgu=d_wgu, wdown=d_wdown, wsgu=d_wsgu, wsdown=d_wsdown, h=d_h, idx=d_idx,
+                             slot=d_slot, wt=d_wt)
                 ctx.flush()
                 idx = d_idx.read(np.uint32, (T_local, K))
                 slot = d_slot.read(np.uint32, (T_local, K))
@@ -68,7 +73,7 @@ def main():
                 good = (np.array_equal(idx, full.idx[lo:hi]) and np.array_equal(slot, want)
                         and bool(np.all(err <= 1e-3 + 2e-2 * np.abs(full.h[lo:hi, 0]))))
                 if not good:
-                    print(f"rank {rank}: mismatch T{T_local} E{E} mb{nmb} transfer{transfer} rep{rep}: idx {np.array_equal(idx, full.idx[lo:hi])} "
+                    print(f"rank {rank}: mismatch T{T_local} E{E} S{S} mb{nmb} transfer{transfer} rep{rep}: idx {np.array_equal(idx, full.idx[lo:hi])} "
                           f"slot {np.array_equal(slot, want)} max err {err.max():.3e}", flush=True)
                 ok = ok and good
             dist.barrier()
