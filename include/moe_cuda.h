@@ -40,7 +40,16 @@ struct mda_pc_absmax_t { uint32_t n, slot; };                                   
 struct mda_pc_cast_t { uint32_t n, slot; };                                            /* shader/cast_f16.comp:14-17 */
 struct mda_pc_qwen_bf16_t { uint32_t n; };                                             /* src/pc.h:273-275 */
 struct mda_pc_kd_bytes_t { uint32_t rows, vocab; };                                    /* src/pc.h:406-409 */
+struct mda_pc_qwen_norm_t {                                                            /* src/pc.h:283-304 */
+    uint32_t rows, groups, gsize, in_stride, in_off, in_gstride, out_stride, out_off, out_gstride, w_off, wstride, op, rot,
+        seqlen, z_stride, z_off, z_gstride;
+    float eps, scale, theta;
+};
+struct mda_pc_qwen_hc_t { uint32_t rows, d, hc, op, inj_stride, inj_off; };            /* src/pc.h:306-313 */
 #endif
+/* mda_qwen_mm's arguments (src/qwen.c:541-570) that matter here: C[rows x n] = A16[rows x k] * W[n x k]^T, sa = the
+ * scale slot of A's fp16 cast (MDA_PC_NO_SLOT: scale 1). */
+struct moe_pc_dense_t { uint32_t rows, n, k, sa; };
 typedef struct mda_pc_moe_route_t moe_pc_route_t;
 typedef struct mda_pc_moe_scan_t moe_pc_scan_t;
 typedef struct mda_pc_moe_scatter_t moe_pc_scatter_t;
@@ -164,6 +173,27 @@ void moe_cuda_swiglu(moe_cuda_ctx_t *c, const float *a, float *y, struct mda_pc_
 void moe_cuda_absmax(moe_cuda_ctx_t *c, const float *x, uint32_t *amax, struct mda_pc_absmax_t pc); /* shader/absmax.comp, src/qwen.c:858-867 */
 void moe_cuda_cast_f16(moe_cuda_ctx_t *c, const float *src, void *dst, const uint32_t *amax,
                        struct mda_pc_cast_t pc); /* shader/cast_f16.comp, src/qwen.c:868-877 */
+
+/* ---- the steps either side of the MoE path ---------------------------------
+ * The hyper-connection residual mixer that produces a layer's input x and the
+ * injection scalars the combine reads (mda_qwen_res_rec, src/qwen.c:641-663),
+ * and the teacher's head (mda_qwen_head, src/qwen.c:1080-1099: the same mixer,
+ * a cast, the vocabulary product in row chunks, then the sink below).
+ * moe_cuda_swiglu above also takes op 1 of shader/qwen_elem.comp (silu(scale*a)),
+ * moe_cuda_absmax + moe_cuda_cast_f16 are mda_qwen_cast (src/qwen.c:517-539). */
+/* shader/qwen_norm.comp (bindings x, w, y, z), ops 0 and 1: grouped RMSNorm with
+ * weight 1 + w (op 0), or x * scale / sqrt(sum x^2 + 1e-6) (op 1).  z is unused
+ * by these ops and may be NULL. */
+void moe_cuda_norm(moe_cuda_ctx_t *c, const float *x, const float *w, float *y, const float *z,
+                   struct mda_pc_qwen_norm_t pc);
+/* shader/qwen_hc.comp (bindings a, b, h): op 0 the mixer's read-out, op 1 the
+ * stream injection, op 2 h += a + b (mda_qwen_hc, src/qwen.c:615-631). */
+void moe_cuda_hc(moe_cuda_ctx_t *c, const float *a, const float *b, float *h, struct mda_pc_qwen_hc_t pc);
+/* mda_qwen_mm (src/qwen.c:541-570; shader/matmul_f16_wide.comp and the small-tile
+ * kernel it alternates with): dense fp16 x fp16 -> fp32 product on the tcgen05
+ * kernel of the grouped products.  n % 128 == 0, k % 8 == 0; any rows >= 1. */
+void moe_cuda_dense(moe_cuda_ctx_t *c, const void *A16, const void *W, float *C, const uint32_t *amax,
+                    struct moe_pc_dense_t pc);
 
 /* ---- weight upload step ---------------------------------------------------
  * shader/qwen_bf16.comp (binding w; call mda_qwen_convert, src/qwen.c:365-378):

@@ -143,6 +143,70 @@ def swiglu(a, n, astride, ao, bo):
     return y
 
 
+def silu_scaled(a, n, astride, ao, scale):
+    """shader/qwen_elem.comp op 1: y = silu(a[:, ao:ao+n] * scale)."""
+    _chk(a, np.float32, "a")
+    rows = a.size // astride
+    y = np.empty((rows, n), np.float32)
+    lib().moe_ref_silu_scaled(_p(a), _p(y), C.c_uint32(rows), C.c_uint32(n), C.c_uint32(astride), C.c_uint32(ao),
+                              C.c_float(scale))
+    return y
+
+
+def norm(x, w, groups, gsize, op=0, w_off=0, eps=1e-6, scale=1.0):
+    """shader/qwen_norm.comp ops 0 / 1 on x [rows, groups*gsize] with mda_qwen_norm_pc's strides."""
+    _chk(x, np.float32, "x")
+    rows = x.size // (groups * gsize)
+    y = np.empty_like(x)
+    lib().moe_ref_norm(_p(x), _p(w), _p(y), C.c_uint32(rows), C.c_uint32(groups), C.c_uint32(gsize), C.c_uint32(w_off),
+                       C.c_uint32(op), C.c_float(eps), C.c_float(scale))
+    return y
+
+
+def hc(a, b, h, rows, d, n_hc, op, inj_stride=0, inj_off=0):
+    """shader/qwen_hc.comp; h is written (op 0) or accumulated into (ops 1, 2) in place."""
+    _chk(a, np.float32, "a"); _chk(b, np.float32, "b"); _chk(h, np.float32, "h")
+    lib().moe_ref_hc(_p(a), _p(b), _p(h), C.c_uint32(rows), C.c_uint32(d), C.c_uint32(n_hc), C.c_uint32(op),
+                     C.c_uint32(inj_stride), C.c_uint32(inj_off))
+    return h
+
+
+def dense(A16, W16, amax=None, sa=NO_SLOT):
+    """mda_qwen_mm (src/qwen.c:541-570): C[rows, n] = A16[rows, k] * W16[n, k]^T / scale(sa), fp32 accumulate --
+    the grouped product's arithmetic over a dense tile schedule."""
+    rows, k = A16.shape
+    n = W16.shape[0]
+    m = (rows + 127) // 128 * 128
+    Ap = np.zeros((m, k), np.uint16)
+    Ap[:rows] = A16
+    out = mm(Ap, np.ascontiguousarray(W16.reshape(1, n, k)), np.zeros(m // 128, np.uint32), n, k, amax=amax, sa=sa)
+    return out[:rows]
+
+
+def cast(x, amax, slot):
+    """mda_qwen_cast (src/qwen.c:517-539): absmax into the slot, then the fp16 cast with the slot's power-of-two scale."""
+    absmax(x, amax, slot)
+    return cast_f16(x, amax, slot)
+
+
+def res_rec(h, wnorm, wdown16, wup16, n_hc, hc_rank, hc_pad, eps=1e-6):
+    """mda_qwen_res_rec (src/qwen.c:641-663): the hyper-connection mixer.  h fp32 [rows, n_hc, d]; wnorm fp32
+    [n_hc * d] (norm weight rows of the streams); wdown16 fp16 [hc_pad, n_hc*d]; wup16 fp16 [n_hc*d, hc_rank].
+    Returns x [rows, d] (the layer's input), t [rows, hc_pad] (columns hc_rank.. are the injection scalars), hn."""
+    rows, _, d = h.shape
+    d4 = n_hc * d
+    amax = np.zeros(256, np.uint32)
+    hn = norm(np.ascontiguousarray(h.reshape(rows, d4)), wnorm, n_hc, d, op=0, eps=eps)      # :645-647
+    hn16 = cast(hn, amax, 0)                                                                 # :648
+    t = dense(hn16, wdown16, amax, 0)                                                        # :649
+    u = silu_scaled(np.ascontiguousarray(t), hc_rank, hc_pad, 0, 1.0 / n_hc)                 # :650-659
+    u16 = cast(u, amax, 1)                                                                   # :660
+    up = dense(u16, wup16, amax, 1)                                                          # :661
+    x = np.empty((rows, d), np.float32)
+    hc(np.ascontiguousarray(up), hn, x, rows, d, n_hc, 0)                                    # :662
+    return x, t, hn
+
+
 def absmax(x, amax, slot):
     _chk(x, np.float32, "x"); _chk(amax, np.uint32, "amax")
     lib().moe_ref_absmax(_p(x), C.c_uint64(x.size), _p(amax), C.c_uint32(slot))

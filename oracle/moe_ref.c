@@ -207,6 +207,8 @@ void moe_ref_mm(const uint16_t *A, const uint16_t *B, float *C, const uint32_t *
     }
 }
 
+static float moe_ref_sigmoid(float v);
+
 static float moe_ref_silu(float v) { /* shader/qwen_elem.comp:16-18 */
     return v / (1.0f + expf(-v));
 }
@@ -219,6 +221,63 @@ void moe_ref_swiglu(const float *a, float *y, uint32_t rows, uint32_t n, uint32_
         for (uint32_t c = 0; c < n; c += 1) {
             float g = a[(uint64_t)r * astride + ao + c];
             y[(uint64_t)r * n + c] = moe_ref_silu(g) * a[(uint64_t)r * astride + bo + c];
+        }
+    }
+}
+
+/* shader/qwen_elem.comp:20-31 with op == 1: y = silu(a[ao+c] * scale)  (the mixer's gate, src/qwen.c:648-657). */
+void moe_ref_silu_scaled(const float *a, float *y, uint32_t rows, uint32_t n, uint32_t astride, uint32_t ao,
+                         float scale) {
+#pragma omp parallel for schedule(static)
+    for (uint32_t r = 0; r < rows; r += 1) {
+        for (uint32_t c = 0; c < n; c += 1) {
+            y[(uint64_t)r * n + c] = moe_ref_silu(a[(uint64_t)r * astride + ao + c] * scale);
+        }
+    }
+}
+
+/* shader/qwen_norm.comp:63-92 with the contiguous strides of mda_qwen_norm_pc (src/qwen.c:582-604), ops 0 and 1:
+ * per (row, group) ss = sum x^2 (the shader's tree reduction; here a plain sum in ascending c), then
+ * op 0: y = x * rsqrt(ss / gsize + eps) * (1 + w[w_off + g * gsize + c]);  op 1: y = x * scale * rsqrt(ss + 1e-6). */
+void moe_ref_norm(const float *x, const float *w, float *y, uint32_t rows, uint32_t groups, uint32_t gsize,
+                  uint32_t w_off, uint32_t op, float eps, float scale) {
+#pragma omp parallel for schedule(static)
+    for (uint64_t rg = 0; rg < (uint64_t)rows * groups; rg += 1) {
+        const uint32_t g = (uint32_t)(rg % groups);
+        const float *xi = x + rg * gsize;
+        float *yi = y + rg * gsize;
+        float ss = 0.0f;
+        for (uint32_t c = 0; c < gsize; c += 1) ss += xi[c] * xi[c];
+        const float f = op == 1u ? scale / sqrtf(ss + 1e-6f) : 1.0f / sqrtf(ss / (float)gsize + eps);
+        for (uint32_t c = 0; c < gsize; c += 1) {
+            const float wt = op == 0u ? 1.0f + w[w_off + (uint64_t)g * gsize + c] : 1.0f;
+            yi[c] = xi[c] * f * wt;
+        }
+    }
+}
+
+/* shader/qwen_hc.comp:20-39. */
+void moe_ref_hc(const float *a, const float *b, float *h, uint32_t rows, uint32_t d, uint32_t hc, uint32_t op,
+                uint32_t inj_stride, uint32_t inj_off) {
+    if (op == 2u) {
+        for (uint64_t i = 0; i < (uint64_t)rows * d * hc; i += 1) h[i] += a[i] + b[i];
+        return;
+    }
+#pragma omp parallel for schedule(static)
+    for (uint64_t i = 0; i < (uint64_t)rows * d; i += 1) {
+        const uint64_t r = i / d, c = i % d;
+        if (op == 0u) {
+            float acc = 0.0f;
+            for (uint32_t s = 0; s < hc; s += 1) {
+                const uint64_t j = r * hc * d + (uint64_t)s * d + c;
+                acc += moe_ref_sigmoid(a[j]) * b[j];
+            }
+            h[i] = acc / (float)hc;
+        } else {
+            for (uint32_t s = 0; s < hc; s += 1) {
+                const float g = 2.0f * moe_ref_sigmoid(b[r * inj_stride + inj_off + s] / (float)hc);
+                h[r * hc * d + (uint64_t)s * d + c] += a[i] * g;
+            }
         }
     }
 }

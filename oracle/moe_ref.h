@@ -67,6 +67,12 @@ void moe_ref_swiglu(const float *a, float *y, uint32_t rows, uint32_t n, uint32_
                     uint32_t ao, uint32_t bo);
 
 /* shader/absmax.comp:13-31 (atomicMax on the float bits of a non-negative). */
+void moe_ref_silu_scaled(const float *a, float *y, uint32_t rows, uint32_t n, uint32_t astride, uint32_t ao,
+                         float scale); /* shader/qwen_elem.comp op 1 */
+void moe_ref_norm(const float *x, const float *w, float *y, uint32_t rows, uint32_t groups, uint32_t gsize,
+                  uint32_t w_off, uint32_t op, float eps, float scale); /* shader/qwen_norm.comp ops 0, 1 */
+void moe_ref_hc(const float *a, const float *b, float *h, uint32_t rows, uint32_t d, uint32_t hc, uint32_t op,
+                uint32_t inj_stride, uint32_t inj_off); /* shader/qwen_hc.comp */
 void moe_ref_absmax(const float *x, uint64_t n, uint32_t *amax, uint32_t slot);
 
 /* shader/cast_f16.comp:30-35. */

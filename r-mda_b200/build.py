@@ -38,8 +38,10 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
 
 def build_host(force: bool = False) -> str:
     """The C mirror of the reference's call sites and of its weight path, compiled as the reference is (gnu17)."""
-    srcs = [os.path.join(PKG, "host", "moe_host.c"), os.path.join(PKG, "host", "moe_weights.c")]
+    srcs = [os.path.join(PKG, "host", "moe_host.c"), os.path.join(PKG, "host", "moe_weights.c"),
+            os.path.join(PKG, "host", "moe_head.c")]
     deps = srcs + [os.path.join(PKG, "host", "moe_host.h"), os.path.join(PKG, "host", "moe_weights.h"),
+                   os.path.join(PKG, "host", "moe_head.h"),
                    os.path.join(ROOT, "include", "moe_cuda.h")]
     if force or _stale(HOST_LIB, deps) or _stale(HOST_LIB, [LIB]):
         cmd = ["gcc", "-std=gnu17", "-O2", "-Wall", "-Wextra", "-shared", "-fPIC", "-I", os.path.join(ROOT, "include"),

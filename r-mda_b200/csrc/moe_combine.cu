@@ -31,8 +31,7 @@ moe_combine_kernel(moe_combine_args a) {
     __shared__ const YT *s_y[PEER ? MOE_MAX_TOPK : 1];
     __shared__ uint32_t s_mask, s_terms;
     const YT *y = reinterpret_cast<const YT *>(a.y);
-    // One row per block and pass; the expert-parallel layer launches a bounded grid (rows blockIdx.x,
-    // blockIdx.x + gridDim.x, ...) so that the peer loads can share the SMs with a grouped-product CTA.
+    // One row per block and pass (rows blockIdx.x, blockIdx.x + gridDim.x, ...).
     for (uint32_t r = blockIdx.x; r < a.rows; r += gridDim.x) {
         if (PEER && a.per_gpu) {
             // Expert-parallel, one row per owning GPU: every GPU that owns some of the token's experts has
@@ -175,10 +174,10 @@ void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a) {
     if (a.rows == 0) return;
     const bool peer = a.y_peers != NULL;
     MOE_REQUIRE(c, !peer || a.y_is_f16, "combine: peer rows are fp16");
-    // peer loads beside another token slice's products: at most two blocks (512 threads) per SM, which leaves
-    // room for a grouped-product CTA.  Alone on the GPU the kernel wants every row in flight (a bounded grid
-    // measured 115 us against 47 us for the return of one slice over 2 GPUs).
-    const uint32_t grid = a.bounded_grid && a.rows > (uint32_t)c->sm_count * 2u ? (uint32_t)c->sm_count * 2u : a.rows;
+    // One block per row: the peer loads want every row in flight.  (A grid bounded to two blocks per SM, meant to
+    // leave room for another token slice's product CTAs, measured 115 us against 47 us for the return over 2 GPUs
+    // and 0.686 ms against 0.670 ms per layer over 8.)
+    const uint32_t grid = a.rows;
     if (a.y16 != NULL) {
         if (peer) moe_combine_kernel<__half, true, true><<<grid, CB_THREADS, 0, c->stream>>>(a);
         else if (a.y_is_f16) moe_combine_kernel<__half, true, false><<<grid, CB_THREADS, 0, c->stream>>>(a);
@@ -218,26 +217,27 @@ extern "C" void moe_cuda_combine(moe_cuda_ctx_t *c, const float *wt, const uint3
 __device__ __forceinline__ float moe_silu(float v) { return v / (1.0f + expf(-v)); }  // qwen_elem.comp:16-18
 
 __global__ void moe_swiglu_kernel(const float *__restrict__ a, float *__restrict__ y, uint32_t rows, uint32_t n,
-                                  uint32_t astride, uint32_t ao, uint32_t bo) {
+                                  uint32_t astride, uint32_t ao, uint32_t bo, uint32_t op, float scale) {
     size_t total = (size_t)rows * n;
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         size_t r = i / n;
         uint32_t cidx = (uint32_t)(i - r * n);
         float g = a[r * astride + ao + cidx];
-        y[i] = __fmul_rn(moe_silu(g), a[r * astride + bo + cidx]);  // qwen_elem.comp:27
+        if (op == 0u) y[i] = __fmul_rn(moe_silu(g), a[r * astride + bo + cidx]);  // qwen_elem.comp:27
+        else y[i] = moe_silu(__fmul_rn(g, scale));                                // :29 (the mixer's gate, src/qwen.c:648-657)
     }
 }
 
 extern "C" void moe_cuda_swiglu(moe_cuda_ctx_t *c, const float *a, float *y, struct mda_pc_qwen_elem_t pc) {
     if (!MOE_LIVE(c)) return;
-    MOE_REQUIRE(c, pc.op == 0, "swiglu: only op 0 (silu(gate)*up) is part of this path");
+    MOE_REQUIRE(c, pc.op <= 1u, "swiglu: op %u (the shader has 0: silu(gate)*up and 1: silu(scale*a))", pc.op);
     MOE_REQUIRE(c, a != NULL && y != NULL, "swiglu: null buffer");
     size_t total = (size_t)pc.rows * pc.n;
     if (total == 0) return;
     size_t blocks = (total + 255) / 256;
     if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
-    moe_swiglu_kernel<<<(unsigned)blocks, 256, 0, c->stream>>>(a, y, pc.rows, pc.n, pc.astride, pc.ao, pc.bo);
+    moe_swiglu_kernel<<<(unsigned)blocks, 256, 0, c->stream>>>(a, y, pc.rows, pc.n, pc.astride, pc.ao, pc.bo, pc.op, pc.scale);
     MOE_LAUNCHED(c);
 }
 

@@ -116,18 +116,19 @@ void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
                       void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row = NULL,
                       uint32_t *const *src_row_peers = NULL, uint32_t src_base = 0, uint2 *const *ret_peers = NULL,
-                      const float *wt = NULL, bool bounded_grid = false);
+                      const float *wt = NULL);
 
 enum { MOE_MM_F32 = 0, MOE_MM_SWIGLU_F16 = 1, MOE_MM_F16 = 2 };
 // Grouped product.  mode F32: C fp32 [m x n] = A*B^T * s;  SWIGLU_F16: B holds
 // [gate n/2 rows | up n/2 rows] per expert and C fp16 [m x n/2] = silu(gate)*up;
 // F16: C fp16 [m x n].
-// a_rows = rows A really holds (<= m); rows beyond read as zero.  With src_row (SWIGLU_F16 only)
+// a_rows = rows A really holds (<= m); rows beyond read as zero.  c_rows (fp32 mode; 0 = m) = rows C really
+// holds; rows beyond are not stored.  With src_row (SWIGLU_F16 only)
 // A is the un-permuted activation matrix [a_rows x k] and tile row p is its row src_row[p].
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C,
                    const uint32_t *amax, const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k,
                    uint32_t sa, uint32_t sb, uint32_t experts_in_B, uint32_t a_rows, bool prefix = false,
-                   const uint32_t *src_row = NULL);
+                   const uint32_t *src_row = NULL, uint32_t c_rows = 0);
 
 // Weight-stationary grouped product over token chunks (moe_mm_ws.cu).
 void moe_launch_chunks(moe_cuda_ctx *c, const uint32_t *count, const uint32_t *off, uint32_t experts, void *chunks,
@@ -158,7 +159,6 @@ struct moe_combine_args {
     uint32_t world;      // number of GPUs behind y_peers
     uint32_t src_base;
     bool per_gpu;
-    bool bounded_grid;   // launch at most two blocks per SM (the kernel shares the GPU with another slice's products)
 };
 void moe_launch_combine(moe_cuda_ctx *c, const moe_combine_args &a);
 void moe_overlap_prepare_combine(moe_cuda_ctx *c);

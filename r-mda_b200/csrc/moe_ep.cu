@@ -625,9 +625,6 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
     float *wt = L->wt != NULL ? L->wt : ep->wt;
     cudaStream_t main_stream = c->stream;
     const bool prof = c->prof && c->ev_made;
-    // with several token slices in flight the transfer kernels leave room for the other slices' products
-    bool bound = nmb > 1;
-    if (getenv("MOE_EP_BOUND_GRID") != NULL) bound = atoi(getenv("MOE_EP_BOUND_GRID")) != 0;
 
     // stage marks of micro-batch m go on its own stream; moe_cuda_prof_read adds the slices up
     auto mark = [&](uint32_t m, int i) {
@@ -700,7 +697,7 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             // dispatch fused into the scatter: every pair's row goes straight into its owner's expert-contiguous buffer
             moe_launch_place(c, idx + (size_t)row0 * K, ep->dst_off[m], hist + (size_t)(row0 / 8u) * E,
                              (const __half *)L->x16 + (size_t)row0 * d, xin_m, slot + (size_t)row0 * K, rows, K, d / 8u, E,
-                             ep->xin_peer_dev[m], ep->el, NULL, NULL, 0, NULL, NULL, bound);
+                             ep->xin_peer_dev[m], ep->el);
         }
         // dispatch: each row once per destination GPU, then the records of every (token, expert) pair
         if (rows != 0 && ep->per_gpu) {
@@ -773,7 +770,6 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
             a.world = (uint32_t)ep->world;
             a.src_base = (uint32_t)ep->rank * ep->cap;
             a.per_gpu = ep->per_gpu;
-            a.bounded_grid = bound;
             moe_launch_combine(c, a);  // return all-to-all fused into the gather: one partial row per owning GPU
         }
         mark(m, 7);

@@ -52,6 +52,7 @@ struct MmArgs {
     const uint32_t *amax;
     const uint32_t *tiles;
     uint32_t m, n, k, sa, sb, experts_in_B;
+    uint32_t c_rows;  // rows C really holds (<= m): rows beyond are not stored (fp32 mode)
     uint32_t prefix;  // used tiles form a prefix of tiles[]: stop at the first unused one
     // row gather (fused layer): A row p is row src_row[p] of X (~0: padding row, reads as zero)
     const uint32_t *src_row;
@@ -328,6 +329,7 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     tmem_ld32(taddr + cch * 32u, v);
                     tmem_ld_wait();
                     float4 *dst = reinterpret_cast<float4 *>(out + cch * 32u);
+                    if (row >= a.c_rows) continue;
 #pragma unroll
                     for (uint32_t j = 0; j < 8; j += 1) {
                         dst[j] = make_float4(__uint_as_float(v[4 * j]) * scale, __uint_as_float(v[4 * j + 1]) * scale,
@@ -363,7 +365,7 @@ void mm_launch(moe_cuda_ctx *c, const CUtensorMap *tmA, const CUtensorMap *tmB, 
 
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C, const uint32_t *amax,
                    const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k, uint32_t sa, uint32_t sb,
-                   uint32_t experts_in_B, uint32_t a_rows, bool prefix, const uint32_t *src_row) {
+                   uint32_t experts_in_B, uint32_t a_rows, bool prefix, const uint32_t *src_row, uint32_t c_rows) {
     if (!MOE_LIVE(c)) return;
     MOE_REQUIRE(c, A != NULL && B != NULL && C != NULL && tiles != NULL, "mm: null buffer");
     MOE_REQUIRE(c, a_rows >= 1 && a_rows <= m, "mm: a_rows %u outside 1..m", a_rows);
@@ -388,6 +390,8 @@ void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void
     a.sa = sa;
     a.sb = sb;
     a.experts_in_B = experts_in_B;
+    a.c_rows = c_rows == 0 ? m : c_rows;
+    MOE_REQUIRE(c, a.c_rows == m || mode == MOE_MM_F32, "mm: a short C is only supported for fp32 output");
     a.prefix = prefix ? 1u : 0u;
     a.src_row = src_row;
     a.X = (const __half *)A;

@@ -116,8 +116,7 @@ moe_scatter_place_kernel(const uint32_t *__restrict__ idx, const uint32_t *__res
                          uint32_t ppb, uint32_t *__restrict__ src_row, uint32_t *const *__restrict__ src_row_peers,
                          uint32_t src_base, uint2 *const *__restrict__ ret_peers, const float *__restrict__ wt) {
     // ppb = pairs per block (<= SC_MAX_PAIRS): 64 in the stand-alone scatter, 8*topk behind the fused router.
-    // A block takes pair groups blockIdx.x, blockIdx.x + gridDim.x, ...: the expert-parallel layer launches a
-    // bounded grid so that this kernel's peer stores can share the SMs with a resident grouped-product CTA.
+    // A block takes pair groups blockIdx.x, blockIdx.x + gridDim.x, ...
     __shared__ uint32_t s_e[SC_MAX_PAIRS];
     __shared__ uint32_t s_slot[SC_MAX_PAIRS];
     __shared__ uint4 *s_dst[SC_MAX_PAIRS];
@@ -239,14 +238,11 @@ void moe_overlap_prepare_scatter(moe_cuda_ctx *c) {
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
                       void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row, uint32_t *const *src_row_peers,
-                      uint32_t src_base, uint2 *const *ret_peers, const float *wt, bool bounded_grid) {
+                      uint32_t src_base, uint2 *const *ret_peers, const float *wt) {
     if (!MOE_LIVE(c)) return;
     if (rows == 0) return;
     MOE_REQUIRE(c, ((uintptr_t)x16 & 15) == 0 && ((uintptr_t)xp & 15) == 0, "scatter: rows not 16-byte aligned");
     uint32_t nblocks = (rows + 7u) / 8u;
-    // Beside another token slice's products: two blocks (512 threads) per SM at most, so that a grouped-product
-    // CTA still fits beside them; an SM full of these blocks would keep the product waiting.
-    if (bounded_grid && nblocks > (uint32_t)c->sm_count * 2u) nblocks = (uint32_t)c->sm_count * 2u;
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp, slot,
                                                                     rows * topk, topk, d8, experts,
                                                                     (uint4 *const *)xp_peers, experts_per_rank, 8u * topk, src_row,

@@ -50,6 +50,21 @@ class PcBf16(C.Structure):
     _fields_ = [("n", C.c_uint32)]
 
 
+class PcNorm(C.Structure):
+    _fields_ = ([(n, C.c_uint32) for n in ("rows", "groups", "gsize", "in_stride", "in_off", "in_gstride", "out_stride",
+                                             "out_off", "out_gstride", "w_off", "wstride", "op", "rot", "seqlen", "z_stride",
+                                             "z_off", "z_gstride")]
+                + [(n, C.c_float) for n in ("eps", "scale", "theta")])
+
+
+class PcHc(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("rows", "d", "hc", "op", "inj_stride", "inj_off")]
+
+
+class PcDense(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("rows", "n", "k", "sa")]
+
+
 class PcKd(C.Structure):
     _fields_ = [("rows", C.c_uint32), ("vocab", C.c_uint32)]
 
@@ -120,6 +135,9 @@ def lib() -> C.CDLL:
         L.moe_cuda_cast_f16.argtypes = [vp, vp, vp, vp, PcSlot]
         L.moe_cuda_bf16_to_f16.argtypes = [vp, vp, PcBf16]
         L.moe_cuda_kd_bytes.argtypes = [vp, vp, vp, vp, vp, PcKd]
+        L.moe_cuda_norm.argtypes = [vp, vp, vp, vp, vp, PcNorm]
+        L.moe_cuda_hc.argtypes = [vp, vp, vp, vp, PcHc]
+        L.moe_cuda_dense.argtypes = [vp, vp, vp, vp, vp, PcDense]
         L.moe_cuda_moe_rows.restype = u32
         L.moe_cuda_moe_rows.argtypes = [u32, u32, u32]
         L.moe_cuda_layer.argtypes = [vp, C.POINTER(Layer)]
@@ -262,8 +280,20 @@ class Ctx:
         lib().moe_cuda_combine(self.p, _ptr(wt), _ptr(slot), _ptr(y), _ptr(proj), _ptr(sh), _ptr(inj), _ptr(h),
                                PcCombine(rows, d, topk, pstride, sg_off, inj_stride, inj_off, hc))
 
-    def swiglu(self, a, y, rows, n, astride, ao, bo, op=0):
-        lib().moe_cuda_swiglu(self.p, _ptr(a), _ptr(y), PcElem(rows, n, astride, ao, bo, op, 1.0))
+    def swiglu(self, a, y, rows, n, astride, ao, bo, op=0, scale=1.0):
+        lib().moe_cuda_swiglu(self.p, _ptr(a), _ptr(y), PcElem(rows, n, astride, ao, bo, op, scale))
+
+    def norm(self, x, w, y, rows, groups, gsize, op=0, w_off=0, eps=1e-6, scale=1.0):
+        """mda_qwen_norm_pc's strides (src/qwen.c:582-604): contiguous groups, one weight row per group."""
+        pc = PcNorm(rows, groups, gsize, groups * gsize, 0, gsize, groups * gsize, 0, gsize, w_off, gsize, op, 0, 1, 0, 0, 0,
+                    eps, scale, 1.0)
+        lib().moe_cuda_norm(self.p, _ptr(x), _ptr(w), _ptr(y), None, pc)
+
+    def hc(self, a, b, h, rows, d, hc, op, inj_stride=0, inj_off=0):
+        lib().moe_cuda_hc(self.p, _ptr(a), _ptr(b), _ptr(h), PcHc(rows, d, hc, op, inj_stride, inj_off))
+
+    def dense(self, A16, W, Cout, amax, rows, n, k, sa=NO_SLOT):
+        lib().moe_cuda_dense(self.p, _ptr(A16), _ptr(W), _ptr(Cout), _ptr(amax), PcDense(rows, n, k, sa))
 
     def absmax(self, x, amax, n, slot):
         lib().moe_cuda_absmax(self.p, _ptr(x), _ptr(amax), PcSlot(n, slot))

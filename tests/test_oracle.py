@@ -259,3 +259,39 @@ def test_golden_vectors(oracle, synth):
     assert np.allclose(g["wt"], res.wt, rtol=1e-6, atol=0)
     assert np.allclose(g["h_rows"], res.h[::8, 0], rtol=1e-5, atol=1e-7)
     assert np.array_equal(g["xp_rows"], res.xp[:4])
+
+
+def test_mixer_restatement_against_numpy(oracle):
+    """mda_qwen_res_rec's restatement (norm, cast, dense product, silu, cast, dense product, read-out) against the
+    same arithmetic written from the definition in numpy (float64 products of the fp16 operands)."""
+    rng = np.random.default_rng(0)
+    rows, d, nh, rank, pad = 64, 256, 4, 64, 128
+    h = rng.standard_normal((rows, nh, d)).astype(np.float32)
+    wn = (rng.standard_normal(nh * d) * 0.1).astype(np.float32)
+    wd = np.zeros((pad, nh * d), np.float16)
+    wd[:rank + nh] = (rng.standard_normal((rank + nh, nh * d)) * 0.03).astype(np.float16)
+    wu = (rng.standard_normal((nh * d, rank)) * 0.05).astype(np.float16)
+    x, t, hn = oracle.res_rec(h, wn, wd.view(np.uint16), wu.view(np.uint16), nh, rank, pad)
+    hn2 = h / np.sqrt((h * h).mean(-1, keepdims=True) + 1e-6) * (1 + wn.reshape(nh, d))
+    assert np.abs(hn2.reshape(rows, -1) - hn).max() < 1e-5
+    t2 = hn2.reshape(rows, -1).astype(np.float64) @ wd.astype(np.float64).T
+    assert np.abs(t2 - t).max() < 2e-3 * np.abs(t).max()          # the fp16 cast of hn
+    assert np.all(t[:, rank + nh:] == 0)                          # padded weight rows
+    u2 = t2[:, :rank] / nh
+    u2 = u2 / (1 + np.exp(-u2))
+    up2 = u2 @ wu.astype(np.float64).T
+    x2 = (1 / (1 + np.exp(-up2.reshape(rows, nh, d))) * hn2).mean(1)
+    assert np.abs(x2 - x).max() < 1e-3
+
+
+def test_hc_ops_against_numpy(oracle):
+    rng = np.random.default_rng(1)
+    rows, d, nh = 9, 24, 4
+    a = rng.standard_normal((rows, d)).astype(np.float32)
+    b = rng.standard_normal((rows, 16)).astype(np.float32)
+    h0 = rng.standard_normal((rows, nh, d)).astype(np.float32)
+    got = oracle.hc(a, b, h0.copy().reshape(rows, nh * d), rows, d, nh, 1, 16, 5).reshape(rows, nh, d)
+    g = 2.0 / (1.0 + np.exp(-b[:, 5:5 + nh] / nh))
+    assert np.allclose(got, h0 + a[:, None, :] * g[:, :, None], atol=1e-6)
+    a2, b2 = rng.standard_normal((rows, nh * d)).astype(np.float32), rng.standard_normal((rows, nh * d)).astype(np.float32)
+    assert np.allclose(oracle.hc(a2, b2, h0.copy().reshape(rows, nh * d), rows, d, nh, 2), h0.reshape(rows, -1) + a2 + b2, atol=1e-6)
