@@ -405,19 +405,23 @@ static bool stage_open(moe_stage_t *s, moe_cuda_ctx_t *c, uint64_t bytes) {
     return s->host != NULL;
 }
 
-bool moe_bank_open(moe_bank_t *b, moe_cuda_ctx_t *c, moe_bank_cfg_t cfg) {
+bool moe_bank_open_slice(moe_bank_t *b, moe_cuda_ctx_t *c, moe_bank_cfg_t cfg, uint32_t local) {
     memset(b, 0, sizeof(*b));
     b->c = c;
     b->pinned = c != NULL;
-    uint64_t d = cfg.d, e = cfg.experts, i = cfg.inter, s = cfg.shared;
+    uint64_t d = cfg.d, e = cfg.experts, i = cfg.inter, s = cfg.shared, el = local;
     uint64_t dense = ((e + MOE_HOST_PAD_ROWS) * d + 3 * s * d) * sizeof(uint16_t);
     bool ok = stage_open(&b->dense, c, dense);
-    ok = ok && stage_open(&b->gu, c, e * 2 * i * d * sizeof(uint16_t));
-    ok = ok && stage_open(&b->down, c, e * d * i * sizeof(uint16_t));
+    ok = ok && stage_open(&b->gu, c, el * 2 * i * d * sizeof(uint16_t));
+    ok = ok && stage_open(&b->down, c, el * d * i * sizeof(uint16_t));
     if (ok == false) {
         moe_bank_close(b);
     }
     return ok;
+}
+
+bool moe_bank_open(moe_bank_t *b, moe_cuda_ctx_t *c, moe_bank_cfg_t cfg) {
+    return moe_bank_open_slice(b, c, cfg, cfg.experts);
 }
 
 void moe_bank_close(moe_bank_t *b) {
@@ -548,6 +552,42 @@ void moe_bank_put_moe(moe_bank_t *b, const moe_st_set_t *set, const char *prefix
     moe_bank_put(b, &b->down, bank_find(b, set, prefix, l, "mlp.experts.down_proj", (uint64_t)cfg.experts * cfg.d, cfg.inter));
 }
 
+/* rows [lo, hi) of a tensor */
+static moe_st_tensor_t bank_rows(moe_st_tensor_t t, uint64_t lo, uint64_t hi) {
+    if (t.ok && lo <= hi && hi <= t.rows) {
+        t.data += lo * t.cols * sizeof(uint16_t);
+        t.rows = hi - lo;
+    } else {
+        t.ok = false;
+    }
+    return t;
+}
+
+void moe_bank_put_moe_slice(moe_bank_t *b, const moe_st_set_t *set, const char *prefix, moe_bank_cfg_t cfg, uint32_t l,
+                            uint32_t e_lo, uint32_t e_hi) {
+    if (e_lo > e_hi || e_hi > cfg.experts) {
+        fprintf(stderr, "moe_bank: expert slice %u..%u outside 0..%u\n", e_lo, e_hi, cfg.experts);
+        b->fail = true;
+        return;
+    }
+    /* replicated part: exactly mda_qwen_put_moe's dense stage */
+    b->moe = moe_bank_put(b, &b->dense, bank_find(b, set, prefix, l, "mlp.gate.weight", cfg.experts, cfg.d));
+    if (cfg.shared != 0) {
+        moe_bank_put(b, &b->dense, bank_find(b, set, prefix, l, "mlp.shared_expert_gate.weight", 1, cfg.d));
+    }
+    moe_bank_pad_to(b, &b->dense, b->moe, cfg.experts + MOE_HOST_PAD_ROWS, cfg.d);
+    if (cfg.shared != 0) {
+        moe_bank_put(b, &b->dense, bank_find(b, set, prefix, l, "mlp.shared_expert.gate_proj.weight", cfg.shared, cfg.d));
+        moe_bank_put(b, &b->dense, bank_find(b, set, prefix, l, "mlp.shared_expert.up_proj.weight", cfg.shared, cfg.d));
+        b->sdown = moe_bank_put(b, &b->dense, bank_find(b, set, prefix, l, "mlp.shared_expert.down_proj.weight", cfg.d, cfg.shared));
+    }
+    /* sharded part: this rank's rows of the two fused expert tensors */
+    moe_st_tensor_t gu = bank_find(b, set, prefix, l, "mlp.experts.gate_up_proj", (uint64_t)cfg.experts * 2 * cfg.inter, cfg.d);
+    moe_st_tensor_t dn = bank_find(b, set, prefix, l, "mlp.experts.down_proj", (uint64_t)cfg.experts * cfg.d, cfg.inter);
+    moe_bank_put(b, &b->gu, bank_rows(gu, (uint64_t)e_lo * 2 * cfg.inter, (uint64_t)e_hi * 2 * cfg.inter));
+    moe_bank_put(b, &b->down, bank_rows(dn, (uint64_t)e_lo * cfg.d, (uint64_t)e_hi * cfg.d));
+}
+
 static void bank_send(moe_bank_t *b, const moe_stage_t *s, void *dev, bool convert) {
     if (s->used > 0) {
         moe_cuda_write(b->c, dev, s->host, (size_t)s->used); /* mda_qwen_stage_copy, src/qwen.c:356-362 */
@@ -574,7 +614,11 @@ void moe_bank_upload(moe_bank_t *b, void *wd, void *wgu, void *wdown, bool conve
 static void *bank_job_run(void *arg) { /* mda_qwen_load_run, src/qwen.c:488-498 */
     moe_bank_job_t *j = arg;
     moe_bank_reset(j->b);
-    moe_bank_put_moe(j->b, j->set, j->prefix, j->cfg, j->layer);
+    if (j->e_lo == 0 && j->e_hi == 0) {
+        moe_bank_put_moe(j->b, j->set, j->prefix, j->cfg, j->layer);
+    } else {
+        moe_bank_put_moe_slice(j->b, j->set, j->prefix, j->cfg, j->layer, j->e_lo, j->e_hi);
+    }
     return NULL;
 }
 

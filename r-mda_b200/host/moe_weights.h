@@ -94,6 +94,14 @@ uint64_t moe_bank_put(moe_bank_t *b, moe_stage_t *s, moe_st_tensor_t t);      /*
 void moe_bank_pad_to(moe_bank_t *b, moe_stage_t *s, uint64_t start, uint32_t rows, uint32_t cols); /* mda_qwen_pad_to */
 /* mda_qwen_put_moe: the six tensors of layer l, named prefix + "layers.<l>.mlp...." */
 void moe_bank_put_moe(moe_bank_t *b, const moe_st_set_t *set, const char *prefix, moe_bank_cfg_t cfg, uint32_t l);
+/* Expert parallel: rank g of G stages only its experts [e_lo, e_hi) of the two fused expert tensors (rows
+ * [e_lo*2I, e_hi*2I) of gate_up_proj and [e_lo*d, e_hi*d) of down_proj, read straight out of the mapped shard);
+ * the router rows and the shared expert are replicated and staged whole.  The reference is single-device and
+ * always stages all experts (src/qwen.c:441-452, 464-498).  moe_bank_open_slice sizes the expert stages for
+ * `local` experts. */
+bool moe_bank_open_slice(moe_bank_t *b, moe_cuda_ctx_t *c, moe_bank_cfg_t cfg, uint32_t local);
+void moe_bank_put_moe_slice(moe_bank_t *b, const moe_st_set_t *set, const char *prefix, moe_bank_cfg_t cfg, uint32_t l,
+                            uint32_t e_lo, uint32_t e_hi);
 /* mda_qwen_upload: three host-to-device copies, then the bf16 -> fp16 conversion in place.
  * wd / wgu / wdown: device buffers at least as large as the bank's stages. */
 void moe_bank_upload(moe_bank_t *b, void *wd, void *wgu, void *wdown, bool convert_gu);
@@ -106,6 +114,7 @@ typedef struct moe_bank_job_t { /* mda_qwen_job_t: loads one layer on a thread w
     uint32_t layer;
     pthread_t th;
     bool started;
+    uint32_t e_lo, e_hi; /* expert slice to stage; 0, 0 = all experts */
 } moe_bank_job_t;
 void moe_bank_prefetch(moe_bank_job_t *job); /* mda_qwen_prefetch */
 void moe_bank_join(moe_bank_job_t *job);

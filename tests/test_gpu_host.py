@@ -1,5 +1,5 @@
-"""The C host-side mirror of the reference's call sites (r-mda_b200/host/moe_host.c, the patch of
-INTEGRATION.md applied to mda_qwen_route_rec / mda_qwen_moe_rec) driven through ctypes: the
+"""The C host-side mirror of the reference's call sites (r-mda_b200/host/moe_host.c: mda_qwen_route_rec /
+mda_qwen_moe_rec with the dispatch target swapped) driven through ctypes: the
 step-by-step sequence and the fused entry point against the CPU oracle."""
 import ctypes as C
 import dataclasses

@@ -35,7 +35,7 @@ class StTensor(C.Structure):
 
 class BankJob(C.Structure):
     _fields_ = [("b", C.POINTER(Bank)), ("set", C.POINTER(StSet)), ("prefix", C.c_char_p), ("cfg", BankCfg),
-                ("layer", C.c_uint32), ("th", C.c_ulong), ("started", C.c_bool)]
+                ("layer", C.c_uint32), ("th", C.c_ulong), ("started", C.c_bool), ("e_lo", C.c_uint32), ("e_hi", C.c_uint32)]
 
 
 @pytest.fixture(scope="module")
@@ -54,6 +54,9 @@ def wlib(pkg):
     L.moe_bank_close.argtypes = [C.POINTER(Bank)]
     L.moe_bank_reset.argtypes = [C.POINTER(Bank)]
     L.moe_bank_put_moe.argtypes = [C.POINTER(Bank), C.POINTER(StSet), C.c_char_p, BankCfg, C.c_uint32]
+    L.moe_bank_open_slice.restype = C.c_bool
+    L.moe_bank_open_slice.argtypes = [C.POINTER(Bank), C.c_void_p, BankCfg, C.c_uint32]
+    L.moe_bank_put_moe_slice.argtypes = [C.POINTER(Bank), C.POINTER(StSet), C.c_char_p, BankCfg, C.c_uint32, C.c_uint32, C.c_uint32]
     L.moe_bank_upload.argtypes = [C.POINTER(Bank), C.c_void_p, C.c_void_p, C.c_void_p, C.c_bool]
     L.moe_bank_prefetch.argtypes = [C.POINTER(BankJob)]
     L.moe_bank_join.argtypes = [C.POINTER(BankJob)]
@@ -114,6 +117,48 @@ def expected_dense(t, l, d, E, S):
 
 
 @pytest.mark.parametrize("S", [0, 64])
+def test_expert_slice_staging(wlib, tmp_path, S):
+    """Expert parallel: every rank stages the replicated dense block whole and only its own experts' rows of the
+    two fused expert tensors; the slices of all ranks put together are the full tensors."""
+    d, E, I, G = 64, 8, 32, 4
+    rng = np.random.default_rng(5)
+    l0 = layer_tensors(rng, 0, d, E, I, S)
+    write_safetensors(tmp_path / "model.safetensors", l0)
+    st = wlib.moe_st_open_set(str(tmp_path).encode())
+    cfg = BankCfg(d, E, I, S)
+    base = f"{PREFIX}layers.0.mlp."
+    gu_full, down_full = l0[base + "experts.gate_up_proj"][1], l0[base + "experts.down_proj"][1]
+    got_gu, got_down = [], []
+    el = E // G
+    for g in range(G):
+        bank = Bank()
+        assert wlib.moe_bank_open_slice(C.byref(bank), None, cfg, el)
+        assert bank.gu.size == el * 2 * I * d * 2 and bank.down.size == el * d * I * 2
+        if g % 2 == 0:
+            wlib.moe_bank_put_moe_slice(C.byref(bank), C.byref(st), PREFIX.encode(), cfg, 0, g * el, (g + 1) * el)
+        else:   # the loader thread takes the same slice
+            job = BankJob(C.pointer(bank), C.pointer(st), PREFIX.encode(), cfg, 0, 0, False, g * el, (g + 1) * el)
+            wlib.moe_bank_prefetch(C.byref(job))
+            wlib.moe_bank_join(C.byref(job))
+        assert not bank.fail
+        assert np.array_equal(stage_bytes(bank.dense), expected_dense(l0, 0, d, E, S))
+        got_gu.append(stage_bytes(bank.gu).copy())
+        got_down.append(stage_bytes(bank.down).copy())
+        wlib.moe_bank_close(C.byref(bank))
+    assert np.array_equal(np.concatenate(got_gu), gu_full.ravel())
+    assert np.array_equal(np.concatenate(got_down), down_full.ravel())
+    bank = Bank()
+    assert wlib.moe_bank_open_slice(C.byref(bank), None, cfg, el)
+    wlib.moe_bank_put_moe_slice(C.byref(bank), C.byref(st), PREFIX.encode(), cfg, 0, 6, 9)     # beyond the last expert
+    assert bank.fail
+    wlib.moe_bank_reset(C.byref(bank))
+    wlib.moe_bank_put_moe_slice(C.byref(bank), C.byref(st), PREFIX.encode(), cfg, 0, 0, 3)     # more experts than the stages hold
+    assert bank.fail
+    wlib.moe_bank_close(C.byref(bank))
+    wlib.moe_st_free_set(C.byref(st))
+
+
+@pytest.mark.parametrize("S", [0, 64])
 def test_shards_to_bank(wlib, tmp_path, S):
     d, E, I = 64, 8, 32
     rng = np.random.default_rng(3)
@@ -145,7 +190,7 @@ def test_shards_to_bank(wlib, tmp_path, S):
         assert np.array_equal(stage_bytes(bank.down), tens[base + "experts.down_proj"][1].ravel())
         assert bank.moe == 0 and bank.sdown == ((E + 128 + 2 * S) * d if S else 0)
     # the loader thread gives the same bank contents
-    job = BankJob(C.pointer(bank), C.pointer(st), PREFIX.encode(), cfg, 1)
+    job = BankJob(C.pointer(bank), C.pointer(st), PREFIX.encode(), cfg, 1, 0, False, 0, 0)
     wlib.moe_bank_prefetch(C.byref(job))
     wlib.moe_bank_join(C.byref(job))
     assert not bank.fail and np.array_equal(stage_bytes(bank.gu), l1[f"{PREFIX}layers.1.mlp.experts.gate_up_proj"][1].ravel())
