@@ -235,6 +235,8 @@ def run_ours(args):
     if world > 1:
         from bench_ep import run_ep  # noqa: F401  (expert-parallel driver)
         return run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local)
+    if cfg.layers > 1 and args.stream_layers:
+        return run_stream(args, ctx, mc, synth, cfg, stream, local)
     if cfg.layers > 1:
         return run_stack(args, ctx, mc, synth, cfg, stream, local)
     return run_layer(args, ctx, mc, synth, cfg, stream, local)
@@ -600,6 +602,117 @@ def run_stack(args, ctx, mc, synth, cfg, stream, local):
     emit(args, out, ok=parity.get("ok", True))
 
 
+def run_stream(args, ctx, mc, synth, cfg, stream, local):
+    """The teacher's weight streaming (mda_qwen_prefetch / mda_qwen_upload, src/qwen.c:381-394,1101-1134) for
+    `--stream-layers` layers of the stack: the layers' bf16 expert tensors sit in page-locked host memory, the
+    device holds two banks, and layer l+1 is uploaded and converted to fp16 in place on a copy stream while layer l
+    computes.  Reports the streamed time per layer beside the upload alone and the compute alone, and checks that
+    the streamed pass gives bit for bit the output of the same layers run from resident weights."""
+    import torch
+
+    T, K, E, d, I = cfg.T, cfg.K, cfg.E, cfg.d, cfg.I
+    NL = args.stream_layers
+    dev = torch.device("cuda", local)
+    pcols = cfg.pstride
+    import dataclasses
+    layers = stack_weights(torch, dataclasses.replace(cfg, layers=NL), dev)
+    L = mc.lib()
+    host = []
+    for wgu, wdown, wd in layers:   # what the shards hold: bf16
+        hg = torch.empty(wgu.numel(), dtype=torch.int16).pin_memory()
+        hd = torch.empty(wdown.numel(), dtype=torch.int16).pin_memory()
+        hg.copy_(wgu.reshape(-1).float().bfloat16().view(torch.int16))
+        hd.copy_(wdown.reshape(-1).float().bfloat16().view(torch.int16))
+        host.append((hg, hd))
+    # resident fp16 copies of exactly those bf16 values, for the comparison pass
+    resident = [(hg.to(dev).view(torch.bfloat16).half(), hd.to(dev).view(torch.bfloat16).half()) for hg, hd in host]
+    x16 = synth.activations(cfg, 0)
+    d_x0 = ctx.upload(x16)
+    d_xa, d_xb = ctx.alloc(T * d * 2), ctx.alloc(T * d * 2)
+    d_proj = ctx.alloc(T * pcols * 4)
+    d_tiles0 = ctx.zeros(T // 128 * 4)
+    banks = [(ctx.alloc(E * 2 * I * d * 2), ctx.alloc(E * d * I * 2)) for _ in range(2)]
+    up = mc.Ctx(local)
+    s_main = torch.cuda.ExternalStream(ctx.stream(), device=local)
+    s_up = torch.cuda.ExternalStream(up.stream(), device=local)
+    ev_up = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    bank_used = [False, False]
+
+    def upload(l):
+        b = l % 2
+        hg, hd = host[l]
+        if bank_used[b]:
+            s_up.wait_event(ev_done[b])                       # the layer that last used this bank is finished
+        L.moe_cuda_write(up.p, banks[b][0].ptr, hg.data_ptr(), hg.numel() * 2)
+        L.moe_cuda_bf16_to_f16(up.p, banks[b][0].ptr, mc.PcBf16(hg.numel() // 2))
+        L.moe_cuda_write(up.p, banks[b][1].ptr, hd.data_ptr(), hd.numel() * 2)
+        L.moe_cuda_bf16_to_f16(up.p, banks[b][1].ptr, mc.PcBf16(hd.numel() // 2))
+        ev_up[b].record(s_up)
+
+    def layer(l, src, dst, wgu_ptr, wdown_ptr):
+        ctx.mm(src, layers[l][2].data_ptr(), d_proj, None, d_tiles0, T, pcols, d, experts_in_B=1)
+        ctx.layer(rows=T, d=d, experts=E, topk=K, inter=I, shared=0, pstride=pcols, hc=1, proj=d_proj, x16=src,
+                  wgu=wgu_ptr, wdown=wdown_ptr, y16=dst, eps=1e-6, flags=args.flags)
+
+    def streamed():
+        src, dst = d_x0, d_xa
+        upload(0)
+        for l in range(NL):
+            if l + 1 < NL:
+                upload(l + 1)                                 # runs under layer l
+            s_main.wait_event(ev_up[l % 2])
+            layer(l, src, dst, banks[l % 2][0].ptr, banks[l % 2][1].ptr)
+            ev_done[l % 2].record(s_main)
+            bank_used[l % 2] = True
+            src, dst = dst, (d_xb if dst is d_xa else d_xa)
+        return src
+
+    def from_resident():
+        src, dst = d_x0, d_xa
+        for l in range(NL):
+            layer(l, src, dst, resident[l][0].data_ptr(), resident[l][1].data_ptr())
+            src, dst = dst, (d_xb if dst is d_xa else d_xa)
+        return src
+
+    def wall(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            out = fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) * 1e3 / reps, out
+
+    ms_stream, last = wall(streamed, args.steps)
+    y_stream = last.read(np.uint16, (T, d))
+    ms_res, last = wall(from_resident, args.steps)
+    y_res = last.read(np.uint16, (T, d))
+
+    def uploads_only():
+        for l in range(NL):
+            upload(l)
+        return None
+    bank_used[0] = bank_used[1] = False                      # nothing computes now: the uploads run back to back
+    ms_up, _ = wall(uploads_only, args.steps)
+    same = bool(np.array_equal(y_stream, y_res))
+    bytes_layer = (E * 3 * d * I) * 2
+    out = {
+        "metric": "teacher-forward MoE layers with weights streamed from page-locked host memory (ms per layer)",
+        "value": ms_stream / NL, "unit": "ms/layer", "n_gpus": 1, "steps": args.steps, "warmup": 1, "ms_per_step": ms_stream,
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": dict(workload_config(cfg, 1), layers=NL, streamed_bytes_per_layer=bytes_layer),
+        "upload_only_ms_per_layer": ms_up / NL, "compute_only_ms_per_layer": ms_res / NL,
+        "upload_GB/s": bytes_layer / (ms_up / NL * 1e-3) / 1e9,
+        "hidden_ms_per_layer": (ms_up + ms_res - ms_stream) / NL,
+        "parity": {"checked": True, "against": "the same layers from resident weights (whose path is checked against the oracle by --config c4)",
+                   "bit_exact": same, "ok": same},
+    }
+    up.close()
+    ctx.close()
+    emit(args, out, ok=same)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -612,6 +725,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the comparison of a step's result with the CPU oracle")
     ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long run behind the timed steps")
     ap.add_argument("--stack-check-layers", type=int, default=2, help="config c4: leading layers compared with the oracle")
+    ap.add_argument("--stream-layers", type=int, default=0, help="config c4 on one GPU: stream this many layers' weights from host memory instead of keeping the stack resident")
     ap.add_argument("--flags", type=int, default=0, help="MOE_LAYER_* flags passed to moe_cuda_layer")
     ap.add_argument("--micro-batches", type=int, default=0, help="expert parallel: token slices per layer (0 = automatic)")
     ap.add_argument("--ep-transfer", type=int, default=0, help="expert parallel: 0 automatic, 1 one row per pair, 2 one row per owning GPU")

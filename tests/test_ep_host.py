@@ -174,3 +174,50 @@ def test_plan_matches_hand_case():
     assert off0.tolist() == [0, 128] and t0.tolist() == [0]            # expert 1 is empty: no tile
     assert off1.tolist() == [0, 256] and t1.tolist() == [0, 0, 1]
     assert epp.ep_rows(2, 64, 4, 2) == (2 * 64 * 2 + 2 * 127 + 127) // 128 * 128
+
+
+def test_token_slices_cover_the_rows_once():
+    """The slices moe_cuda_ep_layer cuts a rank's tokens into: disjoint, in order, 8-row aligned starts,
+    together exactly the rows -- for every slice count the library accepts, ragged and tiny row counts too."""
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    epp = entry.load_package().ep_plan
+    for rows in (0, 1, 7, 8, 9, 37, 300, 1024, 4096, 4101):
+        for nmb in (1, 2, 3, 4):
+            sl = epp.slices(rows, nmb)
+            assert len(sl) == nmb and sl[0][0] == 0 and sl[-1][1] == rows
+            for (a, b), (c, d) in zip(sl, sl[1:]):
+                assert b == c and a <= b and c <= d
+            assert all(a % 8 == 0 or a == rows for a, _ in sl)
+    assert epp.slices(4096, 2) == [(0, 2048), (2048, 4096)]
+    assert epp.slices(300, 4) == [(0, 80), (80, 160), (160, 240), (240, 300)]
+    assert epp.slices(9, 4) == [(0, 8), (8, 9), (9, 9), (9, 9)]       # later slices may be empty
+
+
+def test_sliced_plan_places_every_pair_once():
+    """With the tokens of every rank cut into slices, each slice has its own counts, plan and buffers: the rows of a
+    slice form, inside every owner's buffer of that slice, the single-device order restricted to the slice."""
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    epp = entry.load_package().ep_plan
+    rng = np.random.default_rng(4)
+    world, T, E, K, nmb = 4, 100, 16, 4, 3
+    el = E // world
+    idx = np.stack([np.stack([rng.permutation(E)[:K] for _ in range(T)]) for _ in range(world)]).astype(np.uint32)
+    for a, b in epp.slices(T, nmb):
+        cnt = np.stack([np.bincount(idx[r, a:b].ravel(), minlength=E) for r in range(world)]).astype(np.uint32)
+        seen = {o: set() for o in range(world)}
+        for r in range(world):
+            dst_off = epp.plan(cnt, r)[0]
+            rows = dst_off[idx[r, a:b]].astype(np.int64) + epp.local_ranks(idx[r, a:b])
+            for o, row in zip((idx[r, a:b] // el).ravel(), rows.ravel()):
+                assert row not in seen[int(o)]
+                seen[int(o)].add(int(row))
+        for o in range(world):
+            off_local, tiles = epp.plan(cnt, o)[1:]
+            tot = cnt[:, o * el:(o + 1) * el].sum(0)
+            want = set()
+            for e in range(el):
+                want |= set(range(int(off_local[e]), int(off_local[e]) + int(tot[e])))
+            assert seen[o] == want                       # exactly the non-padding rows of the owner's tiles
+            assert len(tiles) == int(((tot + 127) // 128).sum())
