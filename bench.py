@@ -37,7 +37,7 @@ RTOL_OUT, ATOL_OUT, RTOL_WT = 2e-2, 1e-3, 1e-5
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, the
 # gate_up grouped product with row gather, at the 30B-A3B shape: one Nsight Compute capture of a
 # full-size launch (no scaling involved).
-NCU_TRAFFIC_BYTES = {"c1": 883223040 + 58677504}
+NCU_TRAFFIC_BYTES = {"c1": 978300000 + 49100000}  # moe_mm_ws_kernel<SWIGLU_F16, pair>, one launch (profiles/)
 
 
 def peaks():
@@ -418,14 +418,15 @@ def run_layer(args, ctx, mc, synth, cfg, stream, local):
     combine_bytes = T * K * d * 2 + T * K * 8 + 2 * T * d * 4   # expert outputs are kept fp16 in the fused layer
     route_bytes = T * E * 4 + T * K * 8 + E * 4
     gbs = lambda b, m: b / (m * 1e-3) / 1e9 if m > 0 else None
-    chunked = bool(args.flags & mc.LAYER_CHUNKED)
+    gu_bytes = E * 2 * I * d * 2 + T * K * d * 2 + T * K * I * 2
+    chunked = not (args.flags & (mc.LAYER_TILED | mc.LAYER_UNFUSED)) and d % 128 == 0
     eff = issue_efficiency(got["count"], chunked)
     stages = {
         "route": {"ms": stage_ms["route"], "GB/s": gbs(route_bytes, stage_ms["route"])},
         "scan": {"ms": stage_ms["scan"]},
         "scatter": ({"ms": stage_ms["scatter"], "GB/s": gbs(scatter_bytes, stage_ms["scatter"]),
                      "frac_hbm": gbs(scatter_bytes, stage_ms["scatter"]) / pk["hbm_gbs"]}
-                    if args.flags & (mc.LAYER_MATERIALIZE_XP | mc.LAYER_CHUNKED) else
+                    if chunked or (args.flags & mc.LAYER_MATERIALIZE_XP) else
                     {"ms": stage_ms["scatter"], "note": "ranks and slot tables only; the gate_up product gathers the rows"}),
         "front_end_ms": stage_ms["route"] + stage_ms["scan"] + stage_ms["scatter"],
         "gate_up": {"ms": stage_ms["gate_up"], "TFLOP/s": tf1, "frac_tensor": tf1 / pk["bf16_tflops"],
@@ -451,8 +452,12 @@ def run_layer(args, ctx, mc, synth, cfg, stream, local):
         "parity": parity,
         "roofline": {"bound": "tensor", "kernel": kernel,
                      "achieved": tf1, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": tf1 / pk["bf16_tflops"],
-                     "traffic": NCU_TRAFFIC_BYTES.get(args.config) if args.flags == 0 else None, "peak_source": pk["source"] + " (burst)",
-                     "flops_per_launch": gemm1_flops, "ms_per_launch": stage_ms["gate_up"]},
+                     "traffic": NCU_TRAFFIC_BYTES.get(args.config) if chunked else None, "peak_source": pk["source"] + " (burst)",
+                     "flops_per_launch": gemm1_flops, "ms_per_launch": stage_ms["gate_up"],
+                     # the same launch against the other roof: weights once, each routed row in once, fp16 result out once
+                     "hbm_view": {"algorithmic_bytes": gu_bytes, "achieved": gbs(gu_bytes, stage_ms["gate_up"]), "peak": pk["hbm_gbs"],
+                                  "unit": "GB/s", "frac": gbs(gu_bytes, stage_ms["gate_up"]) / pk["hbm_gbs"],
+                                  "flop_per_byte": gemm1_flops / gu_bytes, "ridge_flop_per_byte": pk["bf16_tflops"] * 1e3 / pk["hbm_gbs"]}},
         "stages": stages,
     }
     if sustained is not None:

@@ -237,9 +237,10 @@ typedef struct moe_cuda_layer_t {
 } moe_cuda_layer_t;
 #define MOE_LAYER_UNFUSED 1u /* run the reference's kernel sequence step by step (fp32 g, absmax rescale) */
 #define MOE_LAYER_YE_F32 2u  /* keep expert outputs fp32 between the down product and the combine */
-#define MOE_LAYER_CHUNKED 4u /* weight-stationary products over per-expert token chunks (MMA width rounded to 16, tcgen05 cta_group::2 pairs) instead of the reference's 128-row tile schedule; measured on a par with the default at 256 tokens per expert, so opt-in */
-#define MOE_LAYER_NO_PAIR 8u /* with MOE_LAYER_CHUNKED: one CTA per tile instead of tcgen05 cta_group::2 pairs */
-#define MOE_LAYER_MATERIALIZE_XP 16u /* write the permuted activations xp to HBM as the reference does, instead of letting the gate_up product gather the rows of x16 itself */
+#define MOE_LAYER_CHUNKED 4u /* weight-stationary products over per-expert token chunks (MMA width rounded to 16, tcgen05 cta_group::2 pairs): the default whenever d % 128 == 0, so the flag only states it */
+#define MOE_LAYER_NO_PAIR 8u /* weight-stationary products with one CTA per tile instead of tcgen05 cta_group::2 pairs */
+#define MOE_LAYER_MATERIALIZE_XP 16u /* with MOE_LAYER_TILED: write the permuted activations xp to HBM as the reference does, instead of letting the gate_up product gather the rows of x16 itself */
+#define MOE_LAYER_TILED 32u /* the reference's 128-row tile schedule (shader/matmul_f16_moe.comp) for both products instead of the weight-stationary chunks */
 
 /* Rows of scratch the layer needs: round128(rows*topk + experts*127), src/qwen.c:68-70. */
 uint32_t moe_cuda_moe_rows(uint32_t rows, uint32_t topk, uint32_t experts);

@@ -88,8 +88,10 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
     // The fused SwiGLU epilogue pairs 128 gate columns with 128 up columns.
     const bool unfused = (L->flags & MOE_LAYER_UNFUSED) != 0 || I % 128u != 0 || (S != 0 && S % 128u != 0);
     const bool ye32 = unfused || (L->flags & MOE_LAYER_YE_F32) != 0;
-    // default: no permuted copy of the activations; MOE_LAYER_MATERIALIZE_XP keeps the reference's xp
-    const bool gather = !unfused && (L->flags & (MOE_LAYER_CHUNKED | MOE_LAYER_MATERIALIZE_XP)) == 0;
+    // default: weight-stationary products over per-expert chunks; MOE_LAYER_TILED: the reference's 128-row tiles
+    const bool chunked = !unfused && ((L->flags & MOE_LAYER_TILED) == 0 || (L->flags & MOE_LAYER_CHUNKED) != 0) && d % 128u == 0;
+    // tiled: no permuted copy of the activations unless MOE_LAYER_MATERIALIZE_XP asks for the reference's xp
+    const bool gather = !unfused && !chunked && (L->flags & MOE_LAYER_MATERIALIZE_XP) == 0;
 
     Carver measure = {NULL, 0};
     LayerBufs b;
@@ -135,26 +137,20 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
         moe_launch_place(c, idx, off, hist, L->x16, b.xp, slot, R, K, d / 8u, E, NULL, 0, gather ? b.src_row : NULL);
     }
     mark(c, 3);
-    if (!unfused && (L->flags & MOE_LAYER_CHUNKED) != 0) {
+    if (chunked) {
         // weight-stationary products over per-expert token chunks (MMA width rounded to 16, not 128)
         const uint32_t max_chunks = R * K / 256u + E + 1u;
         int pair1 = ((L->flags & MOE_LAYER_NO_PAIR) == 0 && I % 128u == 0) ? 2 : 1;
         int pair2 = ((L->flags & MOE_LAYER_NO_PAIR) == 0 && d % 256u == 0) ? 2 : 1;
-        if (d % 128u != 0) pair2 = 0;  // the down product needs whole 128-row weight tiles
         moe_launch_chunks(c, count, off, E, b.chunks, b.n_chunks, max_chunks);
         moe_launch_mm_ws(c, MOE_MM_SWIGLU_F16, pair1, b.xp, M, L->wgu, E, b.hp16, I, b.chunks, b.n_chunks, max_chunks,
                            2u * I, d);  // :847-877 in one kernel
         mark(c, 4);
-        if (pair2 != 0) {
-            moe_launch_mm_ws(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, pair2, b.hp16, M, L->wdown, E, b.ye, d, b.chunks,
-                               b.n_chunks, max_chunks, d, I);  // :878
-        } else {
-            moe_launch_mm(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, b.hp16, L->wdown, b.ye, NULL, tiles, M, d, I,
-                          MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, E, M, true);
-        }
+        moe_launch_mm_ws(c, ye32 ? MOE_MM_F32 : MOE_MM_F16, pair2, b.hp16, M, L->wdown, E, b.ye, d, b.chunks, b.n_chunks,
+                           max_chunks, d, I);  // :878
         mark(c, 5);
     }
-    if (!unfused && (L->flags & MOE_LAYER_CHUNKED) == 0) {
+    if (!unfused && !chunked) {
         if (gather) {  // the gate_up product fetches the rows of x16 itself; xp is never written
             moe_launch_mm(c, MOE_MM_SWIGLU_F16, L->x16, L->wgu, b.hp16, NULL, tiles, M, 2u * I, d, MDA_PC_NO_SLOT,
                           MDA_PC_NO_SLOT, E, R, true, b.src_row);  // :822-877 in one kernel

@@ -30,7 +30,8 @@ using namespace moe_tc;
 constexpr uint32_t BK = 64;
 constexpr uint32_t W_BYTES = 128 * BK * 2;   // 16 KB: this CTA's 128 weight rows
 constexpr uint32_t MAX_TOK = 256;            // tokens per chunk = MMA N
-constexpr uint32_t WS_THREADS = 224;        // warps: 0 weight loads, 1 MMA issue, 2..5 epilogue, 6 token loads
+constexpr uint32_t WS_THREADS = 352;        // warps: 0 weight loads, 1 MMA issue, 2..5 epilogue, 6 token loads, 7..10 more loads
+constexpr uint32_t NPROD = 3;               // issuing threads per operand, taking K steps in turn
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t ET = 32;                  // tokens per epilogue step (one tcgen05.ld of 32 columns)
 constexpr uint32_t PITCH_SW = 160;           // bytes per token row of the turn-round tile, SwiGLU (64 fp16 + pad)
@@ -163,6 +164,9 @@ __device__ __forceinline__ uint32_t x_rows_loaded(uint32_t half) {
 }
 struct XMaps {
     CUtensorMap m[4];  // boxes of 32, 64, 96 and 128 token rows
+#ifdef MOE_WS_PROF
+    CUtensorMap wc;    // experiment: the weight bank as rows of 512 bytes, 16 KB contiguous per box
+#endif
 };
 
 // Profiling builds: event trace of the first two CTAs (one pair), 8 timestamps per K step, 512 K steps.
@@ -239,15 +243,19 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
-    if (warp == 0 || warp == 6) {
-        // ---------------- TMA producers (both CTAs): warp 0 loads the weight tile, warp 6 the token tile ----------------
-        // Two issuing threads, because a thread is held up for a while by every tile load it issues.  Both follow
-        // the same stage ring; the completion bytes of all four loads of a stage (two CTAs x two operands) are
-        // counted on the leader's full barrier, whose one arrival is the weight producer's expect_tx.
+    if (warp == 0 || warp >= 6) {
+        // ---------------- TMA producers (both CTAs) ----------------
+        // One thread gets at most one tile load issued per ~300 ns, whatever its size (measured: 4 KB to 32 KB
+        // boxes, tiled or untiled, L2 or HBM source; threads of different warps add up).  A K step of the
+        // tensor pipe is shorter than that, so each operand has NPROD issuing threads that take K steps in
+        // turn: warps 0, 7, 9 load weight tiles, warps 6, 8, 10 token tiles.  All follow the same stage ring;
+        // the completion bytes of the four loads of a stage (two CTAs x two operands) are counted on the
+        // leader's full barrier, whose one arrival is the weight producer's expect_tx.
         if (lane == 0) {
-            const bool wprod = warp == 0;
+            const bool wprod = warp == 0 || (warp >= 7 && (warp & 1u) != 0);
+            const uint32_t turn_of = warp < 7 ? 0u : (warp - 5u) / 2u;  // 0, 1, 2: which K steps this thread takes
             const uint32_t dbg = PROF ? a.dbg : 0u;
-            uint32_t s = 0, ph = 0, issued = 0, last_par = 0, step = 0;
+            uint32_t s = 0, ph = 0, issued = 0, last_par = 0, step = 0, gstep = 0;
             long long waited = 0, issue_busy = 0;
             bool ok = true;
             for (uint32_t w = cluster_id; w < total && ok && !(dbg & 512u); w += n_clusters) {
@@ -258,7 +266,10 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                 const uint32_t wbytes = (dbg & 4u) ? 0u : W_BYTES;
                 const int32_t f0 = (int32_t)((it.ft * PAIR + rank) * (MODE == MOE_MM_SWIGLU_F16 ? 64u : 128u));
                 const int32_t xrow = (int32_t)(it.row0 + rank * half);
-                for (uint32_t kb = 0; kb < kblocks; kb += 1) {
+                for (uint32_t kb = 0; kb < kblocks; kb += 1, gstep += 1) {
+                    if (gstep % NPROD != turn_of) continue;
+                    s = gstep % G::STAGES;
+                    ph = (gstep / G::STAGES) & 1u;
                     long long t0 = 0;
                     if (PROF) t0 = clock64();
                     if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, wprod ? 11 : 15, a.wait_ns)) {
@@ -276,7 +287,13 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                     const uint32_t full = PAIR == 2 ? map_to_cta(smem_u32(&bars->full[s]), 0) : smem_u32(&bars->full[s]);
                     if (wprod) {
                         if (rank == 0) mbar_expect_tx(smem_u32(&bars->full[s]), (uint32_t)PAIR * (wbytes + xbytes));
-                        if (wbytes != 0u) {
+                        if (PROF && (dbg & 64u)) {
+#ifdef MOE_WS_PROF
+                            // experiment: same bytes, but each tile one contiguous 16 KB piece of the bank
+                            const uint32_t tile = (it.e * ft_count * PAIR + it.ft * PAIR + rank) * kblocks + kb;
+                            tma_2d<PAIR>(base, &tmX.wc, full, 0, (int32_t)(tile * 32u));
+#endif
+                        } else if (wbytes != 0u) {
                             if (MODE == MOE_MM_SWIGLU_F16) tma_4d<PAIR>(base, &tmW, full, kc, 0, f0, (int32_t)it.e);
                             else tma_2d<PAIR>(base, &tmW, full, kc, (int32_t)(it.e * a.n) + f0);
                         }
@@ -295,11 +312,6 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                     }
                     issued |= 1u << s;
                     last_par = (last_par & ~(1u << s)) | (ph << s);
-                    s += 1;
-                    if (s == G::STAGES) {
-                        s = 0;
-                        ph ^= 1u;
-                    }
                 }
             }
             if (!ok && rank == 0 && wprod) {
@@ -310,7 +322,7 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                     }
                 }
             }
-            if (PROF && a.prof != NULL) {
+            if (PROF && a.prof != NULL && turn_of == 0) {
                 a.prof[blockIdx.x * 16u + (wprod ? 1u : 8u)] = (unsigned long long)waited;
                 a.prof[blockIdx.x * 16u + (wprod ? 9u : 10u)] = (unsigned long long)issue_busy;
             }
@@ -318,10 +330,11 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only) ----------------
-        if (lane == 0 && rank == 0) {
-            uint32_t s = 0, ph = 0, n_item = 0;
+        // The whole warp runs the loop, so that barrier addresses and descriptors are warp-uniform values, and one
+        // elected lane issues; one look at the full barriers covers the whole ring (mbar_ring_wait).
+        if (rank == 0) {
+            uint32_t gstep = 0, n_item = 0, ready = 0;
             long long wait_full = 0, wait_acc = 0;
-            unsigned long long ksteps = 0;
             bool ok = true;
             for (uint32_t w = cluster_id; w < total && ok; w += n_clusters) {
                 WsItem it;
@@ -334,48 +347,49 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + as * MAX_TOK;
                 const uint32_t idesc = umma_idesc(128u * PAIR, it.ntok);
-                for (uint32_t kb = 0; kb < kblocks; kb += 1) {
+                for (uint32_t kb = 0; kb < kblocks; kb += 1, gstep += 1) {
+                    const uint32_t s = gstep % G::STAGES;
                     if (PROF) t0 = clock64();
-                    if (!(PROF && (a.dbg & 512u)) && !mbar_wait(smem_u32(&bars->full[s]), ph, abort, a.status, 13, a.wait_ns)) {
+                    if (!(PROF && (a.dbg & 512u)) && ((ready >> s) & 1u) == 0 &&
+                        !mbar_ring_wait<G::STAGES>(bars->full, gstep, ready, abort, a.status, 13, a.wait_ns)) {
                         ok = false;
                         break;
                     }
+                    ready &= ~(1u << s);
                     if (PROF) {
                         wait_full += clock64() - t0;
-                        ws_trace(a.trace, (uint32_t)ksteps + kb, 4u);
+                        if (lane == 0) ws_trace(a.trace, gstep, 4u);
                     }
                     tc_fence_after();
                     const uint32_t base = stage0 + s * G::STAGE_BYTES;
                     const uint64_t ad = umma_desc(base), bd = umma_desc(base + W_BYTES);
-                    if (!(PROF && (a.dbg & 1u))) {
+                    if (elect_one()) {
+                        if (!(PROF && (a.dbg & 1u))) {
 #pragma unroll
-                        for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
-                            if (PAIR == 2) umma_f16_pair(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-                            else umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
+                                if (PAIR == 2) umma_f16_pair(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                                else umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            }
                         }
+                        if (PROF && (a.dbg & 512u)) {  // experiment: tensor pipe alone, nothing is loaded, no stage hand-off
+                        } else if (PAIR == 2) umma_commit_both(smem_u32(&bars->empty[s]));  // frees the stage in both CTAs
+                        else umma_commit(smem_u32(&bars->empty[s]));
                     }
-                    if (PROF && (a.dbg & 512u)) {  // experiment: tensor pipe alone, nothing is loaded, no stage hand-off
-                    } else if (PAIR == 2) umma_commit_both(smem_u32(&bars->empty[s]));  // frees the stage in both CTAs
-                    else umma_commit(smem_u32(&bars->empty[s]));
-                    if (PROF) ws_trace(a.trace, (uint32_t)ksteps + kb, 5u);
-                    s += 1;
-                    if (s == G::STAGES) {
-                        s = 0;
-                        ph ^= 1u;
-                    }
+                    __syncwarp();
+                    if (PROF && lane == 0) ws_trace(a.trace, gstep, 5u);
                 }
-                if (ok) {
+                if (ok && elect_one()) {
                     if (PAIR == 2) umma_commit_both(smem_u32(&bars->tmem_full[as]));
                     else umma_commit(smem_u32(&bars->tmem_full[as]));
                 }
+                __syncwarp();
                 n_item += 1;
-                ksteps += kblocks;
             }
-            if (PROF && a.prof != NULL) {
+            if (PROF && a.prof != NULL && lane == 0) {
                 a.prof[blockIdx.x * 16u + 2u] = (unsigned long long)wait_full;
                 a.prof[blockIdx.x * 16u + 3u] = (unsigned long long)wait_acc;
                 a.prof[blockIdx.x * 16u + 6u] = n_item;
-                a.prof[blockIdx.x * 16u + 7u] = ksteps;
+                a.prof[blockIdx.x * 16u + 7u] = gstep;
             }
         }
         __syncwarp();
@@ -545,6 +559,8 @@ void ws_launch(moe_cuda_ctx *c, const CUtensorMap *tmW, const XMaps &tmX, WsArgs
     MOE_CUDA_TRY(c, cudaGetSymbolAddress((void **)&a.trace, g_ws_trace));
     const char *dbg = getenv("MOE_WS_DBG");
     a.dbg = dbg != NULL ? (uint32_t)atoi(dbg) : 0u;
+    const char *only = getenv("MOE_WS_PROF_MODE");  // counters of one product only (1: gate_up, 2: down)
+    if (only != NULL && atoi(only) != MODE) a.prof = NULL;
 #else
     constexpr bool PROF = false;
 #endif
@@ -609,6 +625,21 @@ void moe_launch_mm_ws(moe_cuda_ctx *c, int mode, int pair, const void *X, uint32
         if (m == NULL) return;
         tmX.m[i] = *m;
     }
+#ifdef MOE_WS_PROF
+    {
+        cuuint64_t dims[2] = {256, (cuuint64_t)experts_in_W * n * k * 2 / 512};
+        cuuint64_t strides[1] = {512};
+        cuuint32_t box[2] = {256, 32};
+        cuuint32_t estr[2] = {1, 1};
+        typedef CUresult (*enc_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+        CUresult r = ((enc_fn)c->encode_tiled)(&tmX.wc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)W, dims, strides, box, estr,
+                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        MOE_REQUIRE(c, r == CUDA_SUCCESS, "mm_ws: contiguous weight map failed: %d", (int)r);
+    }
+#endif
     WsArgs a;
     a.C = C;
     a.chunks = (const uint4 *)chunks;

@@ -57,6 +57,57 @@ static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, vol
     return true;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {  // never suspends the thread
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}\n" : "=r"(pred));
+    return pred != 0;
+}
+// Whole-warp wait for stage (gstep % STAGES) of a ring of `full` barriers that one consumer drains in order.
+// A look at an mbarrier costs ~150 cycles even when the phase is complete, so one look covers the whole ring:
+// lane l asks about the next use of stage l, and the answers are kept in `ready` (bit per stage) until used.
+// False = gave up (own timeout, or another role raised abort).
+template <uint32_t STAGES>
+static __device__ __noinline__ bool mbar_ring_wait(const uint64_t *full, uint32_t gstep, uint32_t &ready, volatile uint32_t *abort,
+                                                   uint32_t *status, uint32_t site, uint64_t wait_ns) {
+    const uint32_t lane = threadIdx.x & 31u, s = gstep % STAGES;
+    const uint32_t l = lane < STAGES ? lane : 0u;
+    const uint32_t use = gstep + (l + STAGES - s) % STAGES;
+    const uint32_t bar = smem_u32(full + l), parity = (use / STAGES) & 1u;
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    for (;;) {
+        ready = __ballot_sync(0xffffffffu, lane < STAGES && mbar_test_wait(bar, parity));
+        if ((ready >> s) & 1u) return true;
+        spins += 1;
+        if ((spins & 0xffu) == 0) {
+            uint32_t stop = *abort != 0 ? 1u : 0u;
+            uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > wait_ns) stop = 2u;
+            stop = __reduce_max_sync(0xffffffffu, stop);
+            if (stop != 0) {
+                if (stop == 2u && lane == 0) {
+                    *abort = 1;
+                    atomicCAS(status, 0u, (uint32_t)MOE_ERR_TIMEOUT | (site << 8));
+                }
+                return false;
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

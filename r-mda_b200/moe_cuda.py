@@ -13,7 +13,7 @@ from . import build as _build
 NO_SLOT = 0xFFFFFFFF
 TILE = 128
 MOE_OK, MOE_ERR_CUDA, MOE_ERR_ARG, MOE_ERR_NOMEM, MOE_ERR_ROUTE, MOE_ERR_TIMEOUT, MOE_ERR_COMM, MOE_ERR_UNSUPPORTED = range(8)
-LAYER_UNFUSED, LAYER_YE_F32, LAYER_CHUNKED, LAYER_NO_PAIR, LAYER_MATERIALIZE_XP = 1, 2, 4, 8, 16
+LAYER_UNFUSED, LAYER_YE_F32, LAYER_CHUNKED, LAYER_NO_PAIR, LAYER_MATERIALIZE_XP, LAYER_TILED = 1, 2, 4, 8, 16, 32
 PROF_STAGES = ("route", "scan", "scatter", "gate_up", "down", "shared", "combine")
 
 
