@@ -414,7 +414,7 @@ def run_layer(args, ctx, mc, synth, cfg, stream, local):
     gemm2_flops = T * K * 2 * d * I
     tf1 = gemm1_flops / (stage_ms["gate_up"] * 1e-3) / 1e12
     tf2 = gemm2_flops / (stage_ms["down"] * 1e-3) / 1e12
-    scatter_bytes = 2 * T * K * d * 2 + T * K * 8
+    scatter_bytes = T * d * 2 + T * K * d * 2 + T * K * 8   # each token row in once, out once per routed pair
     combine_bytes = T * K * d * 2 + T * K * 8 + 2 * T * d * 4   # expert outputs are kept fp16 in the fused layer
     route_bytes = T * E * 4 + T * K * 8 + E * 4
     gbs = lambda b, m: b / (m * 1e-3) / 1e9 if m > 0 else None

@@ -115,6 +115,9 @@ struct moe_ep_state {
     uint32_t *dst_off[EP_MAX_MB];        // [experts]: first row of this rank's rows in the owner's buffer
     uint32_t *tiles[EP_MAX_MB];          // [mcap/128] local tile schedule
     uint32_t *count[EP_MAX_MB];
+    // weight-stationary products: per micro-batch [el] rows per local expert, [el] first rows, 16 words (chunk count), chunk list
+    uint32_t *wsbuf[EP_MAX_MB];
+    uint32_t max_chunks;
     uint32_t *idx, *slot, *bar;
     float *wt;
     cudaStream_t side[EP_MAX_MB];        // streams of micro-batches 1.. (micro-batch 0 runs on the context's stream)
@@ -180,12 +183,12 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
         if (ep->yout_peer[r] != NULL) cudaIpcCloseMemHandle(ep->yout_peer[r]);
         if (ep->sync_peer[r] != NULL) cudaIpcCloseMemHandle(ep->sync_peer[r]);
     }
-    void *mine[10 + 7 * EP_MAX_MB] = {ep->xin, ep->yout, ep->ye, ep->hp16, ep->sync_peer_dev, ep->sync, ep->idx, ep->slot};
+    void *mine[10 + 8 * EP_MAX_MB] = {ep->xin, ep->yout, ep->ye, ep->hp16, ep->sync_peer_dev, ep->sync, ep->idx, ep->slot};
     size_t n_mine = 8;
     mine[n_mine++] = ep->bar;
     mine[n_mine++] = ep->wt;
     for (uint32_t m = 0; m < EP_MAX_MB; m += 1) {
-        void *per[] = {ep->xin_peer_dev[m], ep->yout_peer_dev[m], ep->srow_peer_dev[m], ep->ret_peer_dev[m], ep->dst_off[m], ep->tiles[m], ep->count[m]};
+        void *per[] = {ep->xin_peer_dev[m], ep->yout_peer_dev[m], ep->srow_peer_dev[m], ep->ret_peer_dev[m], ep->dst_off[m], ep->tiles[m], ep->count[m], ep->wsbuf[m]};
         for (size_t i = 0; i < sizeof(per) / sizeof(per[0]) && n_mine < sizeof(mine) / sizeof(mine[0]); i += 1) mine[n_mine++] = per[i];
     }
     if (ep->streams_made) {
@@ -214,7 +217,7 @@ void moe_ep_teardown(moe_cuda_ctx *c) {
 __global__ void moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch, uint32_t site,
                                    uint32_t table_off, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
                                    uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status,
-                                   uint64_t wait_ns);
+                                   uint64_t wait_ns, uint32_t *__restrict__ lcount, uint32_t *__restrict__ loff);
 
 __global__ void moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4 *__restrict__ x16, uint4 *const *__restrict__ xin_peers,
                                    uint32_t rows, uint32_t topk, uint32_t d8, uint32_t el, uint32_t world, uint32_t src_base);
@@ -292,7 +295,9 @@ extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, in
         ep->dst_off[m] = (uint32_t *)moe_cuda_alloc(c, E * 4);
         ep->tiles[m] = (uint32_t *)moe_cuda_alloc(c, (size_t)(mcap / MOE_TILE) * 4);
         ep->count[m] = (uint32_t *)moe_cuda_alloc(c, E * 4);
+        ep->wsbuf[m] = (uint32_t *)moe_cuda_alloc(c, ((size_t)2 * ep->el + 16) * 4 + 16 + (size_t)(mcap / 256u + ep->el + 1u) * 16);
     }
+    ep->max_chunks = mcap / 256u + ep->el + 1u;
     ep->idx = (uint32_t *)moe_cuda_alloc(c, R * K * 4);
     ep->slot = (uint32_t *)moe_cuda_alloc(c, R * K * 4);
     ep->wt = (float *)moe_cuda_alloc(c, R * K * 4);
@@ -449,7 +454,7 @@ __global__ void __launch_bounds__(512)
 moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_peers, uint32_t epoch, uint32_t site,
                    uint32_t table_off, uint32_t *__restrict__ dst_off, uint32_t *__restrict__ tiles,
                    uint32_t experts, uint32_t world, uint32_t rank, uint32_t el, uint32_t mcap, uint32_t *status,
-                   uint64_t wait_ns) {
+                   uint64_t wait_ns, uint32_t *__restrict__ lcount, uint32_t *__restrict__ loff) {
     __shared__ uint32_t incl_s[512];
     uint32_t e = threadIdx.x;
     if (e < experts) {
@@ -488,6 +493,8 @@ moe_ep_plan_kernel(const uint32_t *__restrict__ my_count, uint32_t *const *sync_
             dst_off[e] = off + before;
             if (owner == rank) {
                 for (uint32_t t = off / MOE_TILE; t < (off + p) / MOE_TILE; t += 1) tiles[t] = e - owner_start;
+                lcount[e - owner_start] = tot;  // the rows of this rank's own experts, for the chunk list
+                loff[e - owner_start] = off;
             }
         }
     }
@@ -685,8 +692,14 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         // counts of every rank + plan (also orders this layer after every peer's previous combine)
         moe_ep_plan_kernel<<<1, 512, 0, c->stream>>>(count, (uint32_t *const *)ep->sync_peer_dev, ep->epoch, site,
                                                      EP_FLAG_WORDS + m * (uint32_t)ep->world * E, ep->dst_off[m], ep->tiles[m], E,
-                                                     (uint32_t)ep->world, (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev, c->wait_ns);
+                                                     (uint32_t)ep->world, (uint32_t)ep->rank, ep->el, mcap, c->dev_status_dev, c->wait_ns,
+                                                     ep->wsbuf[m], ep->wsbuf[m] + ep->el);
         c->launches += 1;
+        // the received rows of an expert are cut into chunks of at most 256 for the weight-stationary products
+        uint32_t *n_chunks = ep->wsbuf[m] + 2u * ep->el;
+        void *chunks = (void *)(((uintptr_t)(n_chunks + 16) + 15u) & ~(uintptr_t)15u);
+        const bool ws = d % 256u == 0 && (L->flags & MOE_LAYER_TILED) == 0;
+        if (ws) moe_launch_chunks(c, ep->wsbuf[m], ep->wsbuf[m] + ep->el, ep->el, chunks, n_chunks, ep->max_chunks);
         if (m == 0 && L->off != NULL && nmb == 1) moe_cuda_copy(c, L->off, ep->dst_off[0], (size_t)E * 4);
         mark(m, 2);
         // stagger: this slice's rows go out once the previous slice's are on their way, under its products
@@ -726,11 +739,21 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
                                                        (uint32_t)ep->rank, site + 1u, ep->epoch, c->dev_status_dev, c->wait_ns);  // all rows landed
         c->launches += 1;
         mark(m, 3);
-        moe_launch_mm(c, MOE_MM_SWIGLU_F16, xin_m, L->wgu, ep->hp16 + (size_t)m * mcap * I, NULL, ep->tiles[m], mcap, 2u * I, d,
-                      MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, ep->in_rows, true, ep->per_gpu ? ep->src_row[m] : NULL);
+        if (ws && !ep->per_gpu) {
+            moe_launch_mm_ws(c, MOE_MM_SWIGLU_F16, 2, xin_m, ep->in_rows, L->wgu, ep->el, ep->hp16 + (size_t)m * mcap * I, I, chunks,
+                             n_chunks, ep->max_chunks, 2u * I, d);
+        } else {
+            moe_launch_mm(c, MOE_MM_SWIGLU_F16, xin_m, L->wgu, ep->hp16 + (size_t)m * mcap * I, NULL, ep->tiles[m], mcap, 2u * I, d,
+                          MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, ep->in_rows, true, ep->per_gpu ? ep->src_row[m] : NULL);
+        }
         mark(m, 4);
-        moe_launch_mm(c, MOE_MM_F16, ep->hp16 + (size_t)m * mcap * I, L->wdown, ye_m, NULL,
-                      ep->tiles[m], mcap, d, I, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);
+        if (ws) {
+            moe_launch_mm_ws(c, MOE_MM_F16, 2, ep->hp16 + (size_t)m * mcap * I, mcap, L->wdown, ep->el, ye_m, d, chunks, n_chunks,
+                             ep->max_chunks, d, I);
+        } else {
+            moe_launch_mm(c, MOE_MM_F16, ep->hp16 + (size_t)m * mcap * I, L->wdown, ye_m, NULL,
+                          ep->tiles[m], mcap, d, I, MDA_PC_NO_SLOT, MDA_PC_NO_SLOT, ep->el, mcap, true);
+        }
         if (ep->per_gpu) {  // return, owner side: one weighted partial row per received token
             const uint32_t slots = (uint32_t)ep->world * ep->cap;
             const uint32_t units = slots * ((d / 8u + 127u) / 128u);  // one warp per (slot, 2 KB piece)

@@ -5,13 +5,9 @@
 // from the per-expert offsets (shader/matmul_f16_moe.comp:70-78).
 //
 // One persistent CTA per SM walks the (row tile, column tile) list.  Roles:
-//   warp 0 and the last warps: TMA producers.  A stage is a 128x64 fp16 box
-//              of A and two 128x64 boxes of B in a 4-stage shared-memory ring
-//              (128-byte swizzle); plain per-CTA loads, never multicast.  One
-//              thread gets at most one tile load issued per ~300 ns whatever
-//              the box size (measured on B200), a K step of the tensor pipe
-//              takes ~330 ns, so every box of a stage has its own issuing
-//              threads, NTURN of them taking K steps in turn.
+//   warp 0     TMA producer: 128x64 fp16 boxes of A and two 128x64 boxes of B
+//              per stage into a 4-stage shared-memory ring (128-byte swizzle);
+//              plain per-CTA loads, never multicast.
 //   warp 1     allocates tensor memory and issues tcgen05.mma (M128 N256 K16,
 //              fp16 x fp16 -> fp32) into one of two 256-column accumulators.
 //   warps 2-5  epilogue: tcgen05.ld the finished accumulator, apply the mode's
@@ -39,17 +35,6 @@ constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t BH_BYTES = 128 * BK * 2;     // half of the B tile
 constexpr uint32_t STAGE_BYTES = A_BYTES + 2 * BH_BYTES;
 constexpr uint32_t MM_THREADS = 192;
-#ifndef MM_NTURN
-#define MM_NTURN 2
-#endif
-constexpr uint32_t NTURN = MM_NTURN;            // issuing threads per box of a stage
-template <bool GATHER>
-struct Roles {
-    static constexpr uint32_t BOXES = GATHER ? 2u : 3u;           // B half 0, B half 1, (A)
-    static constexpr uint32_t PRODUCERS = BOXES * NTURN;          // warp 0 is producer 0
-    static constexpr uint32_t FIRST_EXTRA = GATHER ? 10u : 6u;    // producers 1.. are the warps from here on
-    static constexpr uint32_t THREADS = MM_THREADS + (GATHER ? 128u : 0u) + (PRODUCERS - 1u) * 32u;
-};
 constexpr uint32_t TMEM_COLS = 512;
 
 struct __align__(8) MmBarriers {
@@ -76,13 +61,6 @@ struct MmArgs {
     uint32_t *status;
     uint64_t wait_ns;
 };
-
-#ifdef MOE_MM_PROF
-__device__ unsigned long long g_mm_prof[256 * 8];
-#define MMP(x) x
-#else
-#define MMP(x)
-#endif
 
 struct WorkItem {
     uint32_t mt, nt, e, nvalid;
@@ -113,7 +91,7 @@ __device__ __forceinline__ bool mm_work(const MmArgs &a, uint32_t w, uint32_t nt
 // swizzle TMA would apply -- so the permuted copy of the activations never has
 // to exist in HBM.  The weights still arrive by TMA from warp 0.
 template <int MODE, bool GATHER>
-__global__ void __launch_bounds__(Roles<GATHER>::THREADS, 1)
+__global__ void __launch_bounds__(MM_THREADS + (GATHER ? 128 : 0), 1)
 moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, MmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -128,7 +106,7 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; s += 1) {
-            mbar_init(smem_u32(&bars->full[s]), Roles<GATHER>::BOXES + (GATHER ? 128u : 0u));  // one TMA thread per box + every gather thread
+            mbar_init(smem_u32(&bars->full[s]), GATHER ? 129 : 1);  // TMA thread + every gather thread
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (uint32_t s = 0; s < 2; s += 1) {
@@ -149,14 +127,11 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
-    using R = Roles<GATHER>;
-    if (warp == 0 || warp >= R::FIRST_EXTRA) {
-        // ---------------- TMA producers ----------------
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
         if (lane == 0) {
-            const uint32_t pi = warp == 0 ? 0u : warp - R::FIRST_EXTRA + 1u;
-            const uint32_t box = pi % R::BOXES, turn_of = pi / R::BOXES;  // box 0, 1: halves of the B tile; 2: the A tile
-            uint32_t gstep = 0;
-            uint32_t issued = 0;  // bit s set once stage s has a load of this thread in flight or done
+            uint32_t s = 0, ph = 0;
+            uint32_t issued = 0;  // bit s set once stage s has a load in flight or done
             uint32_t last_par = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
@@ -165,29 +140,24 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     if (a.prefix) break;
                     continue;
                 }
-                for (uint32_t kb = 0; kb < kblocks; kb += 1, gstep += 1) {
-                    if (gstep % NTURN != turn_of) continue;
-                    const uint32_t s = gstep % STAGES, ph = (gstep / STAGES) & 1u;
+                for (uint32_t kb = 0; kb < kblocks; kb += 1) {
                     if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort, a.status, 1, a.wait_ns)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t full = smem_u32(&bars->full[s]);
-                    const uint32_t base = stage0 + s * STAGE_BYTES;
-                    if (box == 2u) {
-                        mbar_expect_tx(full, A_BYTES);
-                        tma_load_2d(base, &tmA, full, (int32_t)(kb * BK), (int32_t)(it.mt * BM));
-                    } else if (box == 0u) {
-                        mbar_expect_tx(full, BH_BYTES);
-                        tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
-                    } else if (it.nvalid == BN) {
-                        mbar_expect_tx(full, BH_BYTES);
-                        tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb1);
-                    } else {
-                        mbar_arrive(full);  // a 128-wide last tile has no second half
-                    }
+                    uint32_t full = smem_u32(&bars->full[s]);
+                    uint32_t base = stage0 + s * STAGE_BYTES;
+                    mbar_expect_tx(full, (GATHER ? 0u : A_BYTES) + (it.nvalid == BN ? 2 * BH_BYTES : BH_BYTES));
+                    if (!GATHER) tma_load_2d(base, &tmA, full, (int32_t)(kb * BK), (int32_t)(it.mt * BM));
+                    tma_load_2d(base + A_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb0);
+                    if (it.nvalid == BN) tma_load_2d(base + A_BYTES + BH_BYTES, &tmB, full, (int32_t)(kb * BK), it.rb1);
                     issued |= 1u << s;
                     last_par = (last_par & ~(1u << s)) | (ph << s);
+                    s += 1;
+                    if (s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
                 }
             }
             if (!ok) {
@@ -203,61 +173,49 @@ moe_mm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        // The whole warp runs the loop, so that barrier addresses and descriptors are warp-uniform values, and one
-        // elected lane issues.  Issued from a lone lane of a diverged warp, a K step of 4 MMAs, a barrier wait and
-        // a commit took the thread longer (~510 ns) than the tensor pipe needs for it (~340 ns).
-        uint32_t gstep = 0, n_item = 0, ready = 0;
-        bool ok = true;
-        MMP(long long p_acc = 0; long long p_ring = 0; long long p_issue = 0; long long p_begin = clock64(); long long p_t;)
-        for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
-            WorkItem it;
-            if (!mm_work<MODE>(a, w, nt_count, it)) {
-                if (a.prefix) break;
-                continue;
-            }
-            const uint32_t as = n_item & 1u, aph = (n_item >> 1) & 1u;
-            MMP(p_t = clock64();)
-            if (!mbar_wait(smem_u32(&bars->tmem_empty[as]), aph ^ 1u, abort, a.status, 2, a.wait_ns)) break;
-            MMP(p_acc += clock64() - p_t;)
-            tc_fence_after();
-            const uint32_t tmem_d = tmem_base + as * BN;
-            const uint32_t idesc = umma_idesc(BM, it.nvalid);
-            for (uint32_t kb = 0; kb < kblocks; kb += 1, gstep += 1) {
-                const uint32_t s = gstep % STAGES;
-                MMP(p_t = clock64();)
-                if (((ready >> s) & 1u) == 0 && !mbar_ring_wait<STAGES>(bars->full, gstep, ready, abort, a.status, 3, a.wait_ns)) {
-                    ok = false;
-                    break;
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0, n_item = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                WorkItem it;
+                if (!mm_work<MODE>(a, w, nt_count, it)) {
+                    if (a.prefix) break;
+                    continue;
                 }
-                MMP(p_ring += clock64() - p_t; p_t = clock64();)
-                ready &= ~(1u << s);
-                // gathered rows were written through the generic proxy; the tensor core reads through the async one
-                if (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                uint32_t as = n_item & 1u, aph = (n_item >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&bars->tmem_empty[as]), aph ^ 1u, abort, a.status, 2, a.wait_ns)) break;
                 tc_fence_after();
-                const uint32_t base = stage0 + s * STAGE_BYTES;
-                const uint64_t ad = BK == 64 ? umma_desc(base) : umma_desc_sw64(base);
-                const uint64_t bd = BK == 64 ? umma_desc(base + A_BYTES) : umma_desc_sw64(base + A_BYTES);
-                if (elect_one()) {
+                uint32_t tmem_d = tmem_base + as * BN;
+                uint32_t idesc = umma_idesc(BM, it.nvalid);
+                for (uint32_t kb = 0; kb < kblocks; kb += 1) {
+                    if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort, a.status, 3, a.wait_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    // gathered rows were written through the generic proxy; the tensor core reads through the async one
+                    if (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    tc_fence_after();
+                    uint32_t base = stage0 + s * STAGE_BYTES;
+                    uint64_t ad = BK == 64 ? umma_desc(base) : umma_desc_sw64(base);
+                    uint64_t bd = BK == 64 ? umma_desc(base + A_BYTES) : umma_desc_sw64(base + A_BYTES);
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / 16; kk += 1) {
                         // +32 bytes per K=16 step inside the 128-byte swizzle row
                         umma_f16(tmem_d, ad + 2ull * kk, bd + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&bars->empty[s]));  // frees the stage when these MMAs retire
+                    s += 1;
+                    if (s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
                 }
-                __syncwarp();
-                MMP(p_issue += clock64() - p_t;)
+                if (ok) umma_commit(smem_u32(&bars->tmem_full[as]));
+                n_item += 1;
             }
-            if (ok && elect_one()) umma_commit(smem_u32(&bars->tmem_full[as]));
-            __syncwarp();
-            n_item += 1;
         }
-        MMP(if (lane == 0 && blockIdx.x < 256) {
-            unsigned long long *o = g_mm_prof + blockIdx.x * 8;
-            o[0] = (unsigned long long)(clock64() - p_begin); o[1] = (unsigned long long)p_acc; o[2] = (unsigned long long)p_ring;
-            o[3] = (unsigned long long)p_issue; o[4] = gstep; o[5] = n_item;
-        })
-    } else if (GATHER && warp >= 6 && warp < 10) {
+        __syncwarp();
+    } else if (GATHER && warp >= 6) {
         // ---------------- row gather (warps 6..9) ----------------
         // CPR = 16-byte chunks per operand row and stage.  Thread g of the 128 handles chunk g % CPR of rows
         // g / CPR + RPI * j: consecutive lanes fetch consecutive chunks of a row, so requests are whole
@@ -399,15 +357,11 @@ void mm_launch(moe_cuda_ctx *c, const CUtensorMap *tmA, const CUtensorMap *tmB, 
         MOE_CUDA_TRY(c, cudaFuncSetAttribute(moe_mm_kernel<MODE, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MM_SMEM));
         c->mm_attr_set[slot] = true;
     }
-    moe_mm_kernel<MODE, GATHER><<<grid, Roles<GATHER>::THREADS, MM_SMEM, c->stream>>>(*tmA, *tmB, a);
+    moe_mm_kernel<MODE, GATHER><<<grid, MM_THREADS + (GATHER ? 128 : 0), MM_SMEM, c->stream>>>(*tmA, *tmB, a);
     MOE_LAUNCHED(c);
 }
 
 }  // namespace
-
-#ifdef MOE_MM_PROF
-extern "C" void moe_mm_prof_read(unsigned long long *out, int words) { cudaMemcpyFromSymbol(out, g_mm_prof, (size_t)words * 8); }
-#endif
 
 void moe_launch_mm(moe_cuda_ctx *c, int mode, const void *A, const void *B, void *C, const uint32_t *amax,
                    const uint32_t *tiles, uint32_t m, uint32_t n, uint32_t k, uint32_t sa, uint32_t sb,

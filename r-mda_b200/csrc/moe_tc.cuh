@@ -87,11 +87,13 @@ static __device__ __noinline__ bool mbar_ring_wait(const uint64_t *full, uint32_
     const uint32_t bar = smem_u32(full + l), parity = (use / STAGES) & 1u;
     uint32_t spins = 0;
     uint64_t t0 = 0;
+    const uint32_t bar_s = smem_u32(full + s), parity_s = (gstep / STAGES) & 1u;
     for (;;) {
         ready = __ballot_sync(0xffffffffu, lane < STAGES && mbar_test_wait(bar, parity));
         if ((ready >> s) & 1u) return true;
+        mbar_try_wait(bar_s, parity_s);  // not there yet: let the hardware park the warp on the stage it needs
         spins += 1;
-        if ((spins & 0xffu) == 0) {
+        if ((spins & 0xfu) == 0) {
             uint32_t stop = *abort != 0 ? 1u : 0u;
             uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;

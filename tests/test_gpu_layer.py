@@ -45,8 +45,7 @@ def check(res, ref):
     return float(err.max())
 
 
-# 0 fused (row gather), 2 fp32 expert outputs, 1 reference sequence, 16 materialised xp, 4 / 12 chunked products
-@pytest.mark.parametrize("flags", [0, 2, 1, 8, 10, 32, 34, 48])  # default (chunked pairs), fp32 ye, unfused, no pairs, tiled, tiled + xp
+@pytest.mark.parametrize("flags", [0, 2, 1, 8, 10, 16, 24, 32, 34, 48])  # default (chunked pairs, row gather), fp32 ye, unfused, no pairs, materialised xp, tiled, tiled + xp
 def test_c0_tiny(ctx, mc, synth, oracle, flags):
     cfg = synth.CONFIGS["c0"]
     inp = synth.layer_inputs(cfg, 0)
@@ -62,7 +61,7 @@ def test_c0_accumulates_into_h(ctx, mc, synth, oracle):
     check(run_layer(ctx, mc, cfg, inp, 0, h0), ref)
 
 
-@pytest.mark.parametrize("name,flags", [("c1", 0), ("c1", 1), ("c1", 8), ("c1", 32), ("c1", 48), ("c3", 0), ("c3", 32), ("c3b", 0), ("c3b", 32)])
+@pytest.mark.parametrize("name,flags", [("c1", 0), ("c1", 1), ("c1", 8), ("c1", 16), ("c1", 32), ("c1", 48), ("c3", 0), ("c3", 32), ("c3b", 0), ("c3b", 32)])
 def test_30b_shape(ctx, mc, synth, oracle, name, flags):
     cfg = synth.CONFIGS[name]
     inp = synth.layer_inputs(cfg, 0)
