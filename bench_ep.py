@@ -408,7 +408,9 @@ def run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local):
                 ret_bytes = remote_rows * d * 2                       # one fp16 partial row per (token, owning GPU)
             else:
                 disp_bytes = ret_bytes = remote_pairs * d * 2         # one row per (token, expert) pair each way
-            out["roofline"] = {"bound": "tensor", "kernel": "moe_mm_kernel<SWIGLU_F16> (gate_up grouped product), rank 0",
+            gu_kernel = ("moe_mm_kernel<SWIGLU_F16, GATHER> (gate_up grouped product over the received rows, 128-row tiles), rank 0" if per_gpu
+                         else "moe_mm_ws_kernel<SWIGLU_F16, pair> (gate_up grouped product over chunks of the received rows), rank 0")
+            out["roofline"] = {"bound": "tensor", "kernel": gu_kernel,
                                "achieved": tf1, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": tf1 / pk["bf16_tflops"],
                                "traffic": None, "peak_source": pk["source"] + " (burst)",
                                "flops_per_launch": gemm1_flops / eff_mb, "launches_per_step": eff_mb, "ms_per_step_all_launches": stage_ms["gate_up"]}
