@@ -225,6 +225,23 @@ __global__ void moe_ep_send_kernel(const uint32_t *__restrict__ idx, const uint4
 __global__ void moe_ep_partial_kernel(const uint2 *__restrict__ ret_tab, const uint4 *__restrict__ ye, uint4 *__restrict__ part,
                                       uint32_t slots, uint32_t topk, uint32_t d8);
 
+// Per-GPU scheme, owner side: the received rows (one per token) copied into expert order, one warp per row, so that
+// the weight-stationary gate_up product can load them as tiles.  Padding rows (~0) are left as they are: a padding
+// row only ever feeds padding rows.
+__global__ void __launch_bounds__(256)
+moe_ep_permute_kernel(const uint32_t *__restrict__ src_row, const uint4 *__restrict__ xin, uint4 *__restrict__ xp, uint32_t rows,
+                      uint32_t d8) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t p = warp; p < rows; p += nwarps) {
+        const uint32_t src = src_row[p];
+        if (src == ~0u) continue;
+        const uint4 *in = xin + (size_t)src * d8;
+        uint4 *out = xp + (size_t)p * d8;
+        for (uint32_t c0 = lane; c0 < d8; c0 += 32u) out[c0] = __ldg(in + c0);
+    }
+}
+
 // Joins the communicator, allocates the peer-visible buffers for the stated
 // maximum shape and maps every peer's buffers.  Collective over all ranks.
 extern "C" void moe_cuda_ep_init(moe_cuda_ctx_t *c, const void *unique_id128, int rank, int world,
@@ -741,6 +758,13 @@ extern "C" void moe_cuda_ep_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) 
         mark(m, 3);
         if (ws && !ep->per_gpu) {
             moe_launch_mm_ws(c, MOE_MM_SWIGLU_F16, 2, xin_m, ep->in_rows, L->wgu, ep->el, ep->hp16 + (size_t)m * mcap * I, I, chunks,
+                             n_chunks, ep->max_chunks, 2u * I, d);
+        } else if (ws) {
+            // per-GPU scheme: the received rows go into expert order first; ye's buffer is free until the down product
+            moe_ep_permute_kernel<<<(mcap + 7u) / 8u, 256, 0, c->stream>>>(ep->src_row[m], (const uint4 *)xin_m, (uint4 *)ye_m, mcap,
+                                                                          d / 8u);
+            c->launches += 1;
+            moe_launch_mm_ws(c, MOE_MM_SWIGLU_F16, 2, ye_m, mcap, L->wgu, ep->el, ep->hp16 + (size_t)m * mcap * I, I, chunks,
                              n_chunks, ep->max_chunks, 2u * I, d);
         } else {
             moe_launch_mm(c, MOE_MM_SWIGLU_F16, xin_m, L->wgu, ep->hp16 + (size_t)m * mcap * I, NULL, ep->tiles[m], mcap, 2u * I, d,
