@@ -228,10 +228,14 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = entry.load_package()
     mc, synth = pkg.moe_cuda, pkg.synth
-    cfg = synth.CONFIGS[args.config]
     stream = torch.cuda.Stream(device=local)
     ctx = mc.Ctx(local, stream.cuda_stream)
     ctx.check()
+    if args.config == "kd":
+        if world > 1:
+            raise SystemExit("--config kd is a one-GPU leg")
+        return run_kd(args, ctx, mc, stream, local)
+    cfg = synth.CONFIGS[args.config]
     if world > 1:
         from bench_ep import run_ep  # noqa: F401  (expert-parallel driver)
         return run_ep(args, ctx, mc, synth, cfg, stream, rank, world, local)
@@ -466,6 +470,66 @@ def run_layer(args, ctx, mc, synth, cfg, stream, local):
         out["cpu_baseline"] = cpu
     for cx in extra:
         cx.close()
+    ctx.close()
+    emit(args, out, ok=parity.get("ok", True))
+
+
+def run_kd(args, ctx, mc, stream, local):
+    """The distillation sink next to the layer (moe_cuda_kd_bytes = shader/kd_bytes.comp) on 1024 rows of
+    logits over a 151 936-token byte-level vocabulary of lower-case strings; HBM bound by its algorithmic
+    bytes (every logit once).  A few rows are compared with the CPU oracle."""
+    import torch
+
+    rows, vocab = 1024, 151936
+    pk = peaks()
+    rng = np.random.default_rng(0)
+    tb = rng.integers(97, 123, (vocab, 16)).astype(np.uint8)      # strings of 1..8 bytes
+    length = rng.integers(1, 9, vocab)
+    for k in range(16):
+        tb[length <= k, k] = 0
+    toks = np.ascontiguousarray(np.concatenate([tb.view(np.uint32).reshape(vocab, 4), length[:, None].astype(np.uint32)], 1))
+    cont = np.zeros((rows, 5), np.uint32)
+    cont[:, :4] = rng.integers(97, 123, (rows, 16)).astype(np.uint8).view(np.uint32).reshape(rows, 4)
+    cont[:, 4] = 8
+    dev = torch.device("cuda", local)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    logits = torch.randn((rows, vocab), device=dev, generator=gen, dtype=torch.float32) * 3.0
+    d_t, d_c, d_o = ctx.upload(toks), ctx.upload(cont), ctx.alloc(rows * 128 * 4)
+    fn = lambda: ctx.kd_bytes(logits.data_ptr(), d_t, d_c, d_o, rows, vocab)
+    torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    ctx.flush()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed_steps(torch, stream, fn, args.steps)
+    clocks = sampler.stop()
+    ctx.check()
+    parity = {"checked": False}
+    if not args.no_parity:
+        from oracle import moe_oracle as O
+        O.use_all_cores()
+        nchk = 8
+        got = d_o.read(np.uint32, (rows, 16, 8))[:nchk]
+        ref = O.kd_bytes(np.ascontiguousarray(logits[:nchk].cpu().numpy()), toks, cont[:nchk])
+        pg = (got >> 16).astype(np.uint16).view(np.float16).astype(np.float64)
+        pr = (ref >> 16).astype(np.uint16).view(np.float16).astype(np.float64)
+        close = np.abs(pg - pr) <= 1.5e-3 * pr + 1e-7
+        parity = {"checked": True, "against": "CPU oracle, first %d rows" % nchk, "probabilities_within_1.5e-3_rel": bool(close.all()),
+                  "true_byte_entries_equal": bool(np.array_equal(got[..., 0] & 0xffff, ref[..., 0] & 0xffff)),
+                  "byte_entries_differing": float(((got & 0xffff) != (ref & 0xffff)).mean())}
+        parity["ok"] = parity["probabilities_within_1.5e-3_rel"] and parity["true_byte_entries_equal"] and parity["byte_entries_differing"] < 0.01
+    nbytes = rows * vocab * 4
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    out = {"metric": "distillation sink rows/s (kd_bytes over a byte-level vocabulary)", "value": rows / (ms * 1e-3), "unit": "rows/s",
+           "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": "kd: 1024 rows x 151936 logits, 16 depths x 8 entries out", "l2": "622 MB of logits per step, larger than L2"},
+           "gpu_launches": 2 * args.steps, "clocks": clocks, "parity": parity,
+           "roofline": {"bound": "hbm", "kernel": "moe_kd_bytes_kernel (+ moe_kd_sort_kernel once per call)", "achieved": gbs,
+                        "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                        "peak_source": pk["source"], "bytes_per_launch": nbytes, "ms_per_launch": ms}}
     ctx.close()
     emit(args, out, ok=parity.get("ok", True))
 
@@ -724,7 +788,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c1", choices=["c0", "c1", "c2", "c3", "c3b", "c4"])
+    ap.add_argument("--config", default="c1", choices=["c0", "c1", "c2", "c3", "c3b", "c4", "kd"])
     ap.add_argument("--ref-tokens", type=int, default=1 << 30, help="tokens per CPU sample/step (default: the whole workload, at most 16384)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline leg")
     ap.add_argument("--no-parity", action="store_true", help="skip the comparison of a step's result with the CPU oracle")
