@@ -111,7 +111,8 @@ void moe_launch_route_hist(moe_cuda_ctx *c, const float *proj, uint32_t *idx, fl
                            uint32_t n_a = 0, uint32_t *ones_b = NULL, uint32_t n_b = 0);
 // off / tiles non-NULL: the last block to finish also runs the reference's scan on the fresh counts.
 void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts,
-                               uint32_t *off = NULL, uint32_t *tiles = NULL, uint32_t tile = 0);
+                               uint32_t *off = NULL, uint32_t *tiles = NULL, uint32_t tile = 0, void *chunks = NULL,
+                               uint32_t *n_chunks = NULL, uint32_t max_chunks = 0);
 void moe_launch_place(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *off, const uint32_t *hist, const void *x16,
                       void *xp, uint32_t *slot, uint32_t rows, uint32_t topk, uint32_t d8, uint32_t experts,
                       void *const *xp_peers, uint32_t experts_per_rank, uint32_t *src_row = NULL,
@@ -197,6 +198,40 @@ __device__ __forceinline__ void moe_scan_body(const uint32_t *count, uint32_t *o
         off[e] = lo;                                                // :33
         for (uint32_t t = lo / tile; t < (lo + p) / tile; t += 1) tiles[t] = e;  // :34-36
     }
+}
+
+// The chunk list of the weight-stationary products: every expert's rows cut into chunks of at most MOE_CHUNK_TOK
+// tokens of near-equal size, MMA width rounded up to 16; entry = (expert, first row, MMA width, valid rows).  For a
+// block of at least 512 threads (all threads of the block must call it; thread e < 512 handles expert e).
+#define MOE_CHUNK_TOK 256u
+__device__ __forceinline__ void moe_chunk_body(const uint32_t *count, const uint32_t *off, uint32_t experts, uint4 *chunks,
+                                               uint32_t *n_chunks, uint32_t max_chunks) {
+    __shared__ uint32_t csum[512];
+    const uint32_t e = threadIdx.x;
+    uint32_t cnt = 0, nch = 0;
+    if (e < 512u) {
+        cnt = e < experts ? __ldcg(count + e) : 0u;
+        nch = (cnt + MOE_CHUNK_TOK - 1u) / MOE_CHUNK_TOK;
+        csum[e] = nch;
+    }
+    __syncthreads();
+    for (uint32_t o = 1; o < 512; o <<= 1) {
+        uint32_t v = (e < 512u && e >= o) ? csum[e - o] : 0u;
+        __syncthreads();
+        if (e < 512u) csum[e] += v;
+        __syncthreads();
+    }
+    if (e < 512u && nch != 0) {
+        const uint32_t first = csum[e] - nch;
+        const uint32_t per = ((cnt + nch - 1u) / nch + 15u) & ~15u;
+        const uint32_t row0 = __ldcg(off + e);
+        for (uint32_t j = 0; j < nch; j += 1) {
+            const uint32_t start = j * per;
+            const uint32_t valid = start < cnt ? min(per, cnt - start) : 0u;
+            if (first + j < max_chunks) chunks[first + j] = make_uint4(e, row0 + start, (valid + 15u) & ~15u, valid);
+        }
+    }
+    if (e == 511u) *n_chunks = min(csum[511], max_chunks);
 }
 
 __device__ __forceinline__ float moe_slot_scale(const uint32_t *amax, uint32_t s) {

@@ -132,7 +132,9 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
         moe_launch_route_hist(c, L->proj, idx, wt, hist, R, E, K, L->pstride, tiles, M / MOE_TILE,
                               gather ? b.src_row : NULL, gather ? M : 0u);
         mark(c, 1);
-        moe_launch_colscan_counts(c, hist, count, R, E, off, tiles, MOE_TILE);  // + the scan, in its last block
+        // + the scan and (weight-stationary products) the chunk list, in its last block
+        moe_launch_colscan_counts(c, hist, count, R, E, off, tiles, MOE_TILE, chunked ? b.chunks : NULL, b.n_chunks,
+                                  R * K / 256u + E + 1u);
         mark(c, 2);
         moe_launch_place(c, idx, off, hist, L->x16, b.xp, slot, R, K, d / 8u, E, NULL, 0, gather ? b.src_row : NULL);
     }
@@ -142,7 +144,6 @@ extern "C" void moe_cuda_layer(moe_cuda_ctx_t *c, const moe_cuda_layer_t *L) {
         const uint32_t max_chunks = R * K / 256u + E + 1u;
         int pair1 = ((L->flags & MOE_LAYER_NO_PAIR) == 0 && I % 128u == 0) ? 2 : 1;
         int pair2 = ((L->flags & MOE_LAYER_NO_PAIR) == 0 && d % 256u == 0) ? 2 : 1;
-        moe_launch_chunks(c, count, off, E, b.chunks, b.n_chunks, max_chunks);
         moe_launch_mm_ws(c, MOE_MM_SWIGLU_F16, pair1, b.xp, M, L->wgu, E, b.hp16, I, b.chunks, b.n_chunks, max_chunks,
                            2u * I, d);  // :847-877 in one kernel
         mark(c, 4);

@@ -517,33 +517,13 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if (PROF && a.prof != NULL && threadIdx.x == 0) a.prof[blockIdx.x * 16u] = (unsigned long long)(clock64() - t_begin);
 }
 
-// Cuts every expert's rows into chunks of at most 256 tokens of near-equal size,
-// MMA width rounded up to 16.  One block; thread = expert.
+// The chunk list as a kernel of its own (expert-parallel layer: the counts come from the plan): one block, thread =
+// expert.  The single-GPU layer builds the same list in the last block of its column scan.
+static_assert(MAX_TOK == MOE_CHUNK_TOK, "the chunk list is cut for the MMA width of this kernel");
 __global__ void __launch_bounds__(512)
 moe_chunk_kernel(const uint32_t *__restrict__ count, const uint32_t *__restrict__ off, uint32_t experts,
                  uint4 *__restrict__ chunks, uint32_t *__restrict__ n_chunks, uint32_t max_chunks) {
-    __shared__ uint32_t s[512];
-    uint32_t e = threadIdx.x;
-    uint32_t cnt = e < experts ? count[e] : 0;
-    uint32_t nch = (cnt + MAX_TOK - 1) / MAX_TOK;
-    s[e] = nch;
-    __syncthreads();
-    for (uint32_t o = 1; o < 512; o <<= 1) {
-        uint32_t v = e >= o ? s[e - o] : 0;
-        __syncthreads();
-        s[e] += v;
-        __syncthreads();
-    }
-    uint32_t first = s[e] - nch;
-    if (nch != 0) {
-        uint32_t per = ((cnt + nch - 1) / nch + 15u) & ~15u;
-        for (uint32_t j = 0; j < nch; j += 1) {
-            uint32_t start = j * per;
-            uint32_t valid = start < cnt ? min(per, cnt - start) : 0;
-            if (first + j < max_chunks) chunks[first + j] = make_uint4(e, off[e] + start, (valid + 15u) & ~15u, valid);
-        }
-    }
-    if (e == 511) *n_chunks = min(s[511], max_chunks);
+    moe_chunk_body(count, off, experts, chunks, n_chunks, max_chunks);
 }
 
 #ifdef MOE_WS_PROF

@@ -44,7 +44,7 @@ moe_scatter_hist_kernel(const uint32_t *__restrict__ idx, uint32_t *__restrict__
 __global__ void __launch_bounds__(1024)
 moe_scatter_colscan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fill, uint32_t nblocks,
                            uint32_t ebound, uint32_t *__restrict__ count_out, uint32_t *ticket, uint32_t *off,
-                           uint32_t *tiles, uint32_t tile) {
+                           uint32_t *tiles, uint32_t tile, uint4 *chunks, uint32_t *n_chunks, uint32_t max_chunks) {
     __shared__ uint32_t seg_sum[32][33];
     __shared__ uint32_t s_last;
     uint32_t el = threadIdx.x & 31u, seg = threadIdx.x >> 5;
@@ -104,6 +104,10 @@ moe_scatter_colscan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ f
         if (s_last) {
             __threadfence();
             moe_scan_body(count_out, off, tiles, ebound, tile);
+            if (chunks != NULL) {  // and the chunk list of the weight-stationary products, from the same counts and offsets
+                __syncthreads();
+                moe_chunk_body(count_out, off, ebound, chunks, n_chunks, max_chunks);
+            }
         }
     }
 }
@@ -198,7 +202,7 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
     moe_scatter_hist_kernel<<<nblocks, SC_PAIRS, ebound * sizeof(uint32_t), c->stream>>>(idx, hist, pairs, ebound,
                                                                                          c->dev_status_dev);
     MOE_LAUNCHED(c);
-    moe_scatter_colscan_kernel<<<(ebound + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, fill, nblocks, ebound, NULL, NULL, NULL, NULL, 0);
+    moe_scatter_colscan_kernel<<<(ebound + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, fill, nblocks, ebound, NULL, NULL, NULL, NULL, 0, NULL, NULL, 0);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<nblocks, SC_THREADS, 0, c->stream>>>(idx, off, hist, (const uint4 *)x16, (uint4 *)xp,
                                                                     slot, pairs, topk, d8, ebound,
@@ -209,7 +213,8 @@ void moe_launch_scatter(moe_cuda_ctx *c, const uint32_t *idx, const uint32_t *of
 // Fused front end, after the router wrote the per-8-row tables into `hist`:
 // column scan in place (block bases for the ranking) which also yields count[].
 void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count, uint32_t rows, uint32_t experts,
-                               uint32_t *off, uint32_t *tiles, uint32_t tile) {
+                               uint32_t *off, uint32_t *tiles, uint32_t tile, void *chunks, uint32_t *n_chunks,
+                               uint32_t max_chunks) {
     if (!MOE_LIVE(c)) return;
     if (rows == 0) return;
     uint32_t nblocks = (rows + 7u) / 8u;
@@ -223,7 +228,8 @@ void moe_launch_colscan_counts(moe_cuda_ctx *c, uint32_t *hist, uint32_t *count,
         ticket = c->ticket;
     }
     moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(hist, NULL, nblocks, experts, count,
-                                                                                                 ticket, off, tiles, tile);
+                                                                                                 ticket, off, tiles, tile,
+                                                                                                 (uint4 *)chunks, n_chunks, max_chunks);
     MOE_LAUNCHED(c);
 }
 
@@ -306,7 +312,7 @@ extern "C" void moe_cuda_scatter_noalloc(moe_cuda_ctx_t *c, const uint32_t *idx,
     moe_scatter_hist_kernel<<<(uint32_t)nblocks, SC_PAIRS, experts * sizeof(uint32_t), c->stream>>>(
         idx, table, (uint32_t)pairs, experts, c->dev_status_dev);
     MOE_LAUNCHED(c);
-    moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts, NULL, NULL, NULL, NULL, 0);
+    moe_scatter_colscan_kernel<<<(experts + CS_EXPERTS - 1u) / CS_EXPERTS, 1024, 0, c->stream>>>(table, fill, (uint32_t)nblocks, experts, NULL, NULL, NULL, NULL, 0, NULL, NULL, 0);
     MOE_LAUNCHED(c);
     moe_scatter_place_kernel<<<(uint32_t)nblocks, SC_THREADS, 0, c->stream>>>(
         idx, off, table, (const uint4 *)x16, (uint4 *)xp, slot, (uint32_t)pairs, pc.topk, pc.d8, experts, NULL, 0, SC_PAIRS, NULL, NULL, 0, NULL, NULL);
