@@ -155,15 +155,15 @@ __device__ __forceinline__ bool epi_all(bool ok) {
 }
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// Token rows per TMA box: the smallest of 32, 64, 96, 128 that covers what is left.
-__device__ __forceinline__ uint32_t x_box_rows(uint32_t left) { return left > 96u ? 128u : (left + 31u) & ~31u; }
+// Token rows per TMA box: the smallest multiple of 16 up to 128 that covers what is left.
+__device__ __forceinline__ uint32_t x_box_rows(uint32_t left) { return left > 112u ? 128u : (left + 15u) & ~15u; }
 __device__ __forceinline__ uint32_t x_rows_loaded(uint32_t half) {
     uint32_t rows = 0;
     for (uint32_t done = 0; done < half; done += x_box_rows(half - done)) rows += x_box_rows(half - done);
     return rows;
 }
 struct XMaps {
-    CUtensorMap m[4];  // boxes of 32, 64, 96 and 128 token rows
+    CUtensorMap m[8];  // boxes of 16, 32, ... 128 token rows
 #ifdef MOE_WS_PROF
     CUtensorMap wc;    // experiment: the weight bank as rows of 512 bytes, 16 KB contiguous per box
 #endif
@@ -299,9 +299,9 @@ moe_mm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                         }
                     } else if (xbytes != 0u) {
                         uint32_t done = 0;
-                        while (done < half) {  // boxes of 32, 64, 96 or 128 token rows: at most 31 rows more than needed
+                        while (done < half) {  // boxes of 16, 32, ... 128 token rows: at most 15 rows more than needed
                             const uint32_t rows = x_box_rows(half - done);
-                            tma_2d<PAIR>(base + W_BYTES + done * (BK * 2u), &tmX.m[rows / 32u - 1u], full, kc, xrow + (int32_t)done);
+                            tma_2d<PAIR>(base + W_BYTES + done * (BK * 2u), &tmX.m[rows / 16u - 1u], full, kc, xrow + (int32_t)done);
                             done += rows;
                         }
                     }
@@ -600,8 +600,8 @@ void moe_launch_mm_ws(moe_cuda_ctx *c, int mode, int pair, const void *X, uint32
                                                        : moe_tmap_2d_f16(c, W, (uint64_t)experts_in_W * n, k, 128, BK);
     if (tmW == NULL) return;
     XMaps tmX;
-    for (uint32_t i = 0; i < 4; i += 1) {
-        const CUtensorMap *m = moe_tmap_2d_f16(c, X, rows_x, k, 32u * (i + 1u), BK);
+    for (uint32_t i = 0; i < 8; i += 1) {
+        const CUtensorMap *m = moe_tmap_2d_f16(c, X, rows_x, k, 16u * (i + 1u), BK);
         if (m == NULL) return;
         tmX.m[i] = *m;
     }
