@@ -71,3 +71,13 @@ def test_product_path_does_not_touch_the_oracle():
             if f.endswith((".py", ".c", ".h", ".cu", ".cuh")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "moe_ref" not in text and "moe_oracle" not in text, os.path.join(dirpath, f)
+
+
+def test_layer_flags_match_the_header(mc):
+    """The Python front end's MOE_LAYER_* values are the header's."""
+    text = open(os.path.join(ROOT, "include", "moe_cuda.h")).read()
+    header = {m.group(1): int(m.group(2)) for m in re.finditer(r"#define\s+MOE_LAYER_([A-Z_]+)\s+(\d+)u", text)}
+    assert set(header) == {"UNFUSED", "YE_F32", "CHUNKED", "NO_PAIR", "MATERIALIZE_XP", "TILED"}
+    for name, value in header.items():
+        assert getattr(mc, "LAYER_" + name) == value
+    assert len(set(header.values())) == len(header) and all(v & (v - 1) == 0 for v in header.values())
