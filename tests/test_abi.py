@@ -76,7 +76,7 @@ def test_product_path_does_not_touch_the_oracle():
 def test_layer_flags_match_the_header(mc):
     """The Python front end's MOE_LAYER_* values are the header's."""
     text = open(os.path.join(ROOT, "include", "moe_cuda.h")).read()
-    header = {m.group(1): int(m.group(2)) for m in re.finditer(r"#define\s+MOE_LAYER_([A-Z_]+)\s+(\d+)u", text)}
+    header = {m.group(1): int(m.group(2)) for m in re.finditer(r"#define\s+MOE_LAYER_([A-Z0-9_]+)\s+(\d+)u", text)}
     assert set(header) == {"UNFUSED", "YE_F32", "CHUNKED", "NO_PAIR", "MATERIALIZE_XP", "TILED"}
     for name, value in header.items():
         assert getattr(mc, "LAYER_" + name) == value
